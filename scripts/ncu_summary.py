@@ -4,7 +4,7 @@
     python scripts/ncu_summary.py gpurun_out/prof_x.ncu-rep [...] --out profiles/r1_ncu_full.md
     python scripts/ncu_summary.py --launches gpurun_out/launches_x.csv --out profiles/r1_launches.md
 
-Runs here (no GPU): `ncu -i <rep> --page raw --csv` and `--page source --csv` read the report offline.
+Runs here (no GPU): `ncu -i <rep> --page raw --csv` reads the report offline.
 """
 from __future__ import annotations
 
@@ -61,38 +61,6 @@ def summarise_full(rep: Path):
     return res
 
 
-def stall_summary(rep: Path, top=12):
-    """Aggregate the per-instruction sampling columns of the source page; list the hottest source lines."""
-    rows = ncu_csv(rep, "source")
-    while rows and rows[0][0] != "Address":
-        rows = rows[1:]
-    if not rows:
-        return None
-    hdr = rows[0]
-    idx = {h: i for i, h in enumerate(hdr)}
-    samp_col = "# Samples" if "# Samples" in idx else None
-    stall_cols = [h for h in hdr if h.startswith("stall_") and "Not Issued" not in h]
-    tot = defaultdict(float)
-    lines = []
-    for r in rows[1:]:
-        if len(r) != len(hdr):
-            continue
-        for c in stall_cols:
-            try:
-                tot[c] += float(r[idx[c]] or 0)
-            except ValueError:
-                pass
-        if samp_col:
-            try:
-                s = float(r[idx[samp_col]] or 0)
-            except ValueError:
-                s = 0
-            src = r[idx.get("Source", 1)] if "Source" in idx else ""
-            lines.append((s, src.strip()[:110]))
-    lines.sort(reverse=True)
-    return {"stalls": sorted(tot.items(), key=lambda kv: -kv[1])[:10], "hot": lines[:top], "samp_col": samp_col}
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("reports", nargs="*")
@@ -141,19 +109,6 @@ def main():
                 w = WORKLOADS[args.workloads[k]]
                 traffic[args.workloads[k]] = {"per_gpu": {"B": w["B"], "Hq": w["Hq"], "Hkv": w["Hkv"]},
                                               "dram_bytes_per_launch": int(rd + wr), "capture": args.title or rep.name}
-        st = stall_summary(rep)
-        if st and st["stalls"]:
-            out.append("warp-state samples by stall reason (source page, summed over instructions):\n")
-            for c, v in st["stalls"]:
-                if v > 0:
-                    out.append(f"- {c}: {v:.0f}")
-            out.append("")
-        if st and st["hot"]:
-            out.append(f"hottest source lines by `{st['samp_col']}`:\n")
-            out.append("```")
-            for s, src in st["hot"]:
-                out.append(f"{s:8.0f}  {src}")
-            out.append("```\n")
     Path(args.out).write_text("\n".join(out) + "\n")
     if args.traffic_json and traffic:
         p = Path(args.traffic_json)

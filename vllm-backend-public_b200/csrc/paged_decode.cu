@@ -122,7 +122,7 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t v) {
     asm("{\n\t.reg .b16 lo;\n\tcvt.u16.u32 lo, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(v));
     return r;
 }
-// same for the high 16 bits of `v` (SASS: F2FP...UNPACK_B Rx.H1 -- no shift instruction)
+// same for the high 16 bits of `v`
 __device__ __forceinline__ uint32_t e4m3x2_hi_to_f16x2(uint32_t v) {
     uint32_t r;
     asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}" : "=r"(r) : "r"(v));

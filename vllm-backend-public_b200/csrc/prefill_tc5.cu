@@ -31,7 +31,7 @@
 //              wrapped EVERY tcgen05.mma in an ELECT / R2UR.BROADCAST / BRA.U.ANY loop, ~12 dependent instructions that
 //              the issuing thread -- sharing its scheduler with two softmax warps -- needed 80-105 cycles for, where the
 //              pipe needs 64.  The whole warp now runs the loop with warp-uniform operands and elect.sync picks the lane
-//              per instruction group (what CUTLASS does): 1-3 SASS instructions between UTCHMMAs (1375 TF/s).
+//              per instruction group (what CUTLASS does) (1375 TF/s).
 //   +2.5 %     P is handed over in two halves, so P.V of keys 0-63 runs under the exponentials of keys 64-127 (1409 TF/s,
 //              0.845 of the measured cuBLAS bf16 burst).  Quarters would cost the softmax as much as they save the chain.
 //   small      launches of less than one wave at 256 rows per CTA (a 512-token chunk over a long prefix) run 128 rows per
