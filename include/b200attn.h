@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 1
+#define B2_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define B2_API __attribute__((visibility("default")))
@@ -388,6 +388,11 @@ typedef struct b2_step_plan {
     const int64_t* preempted_ids;       /* recompute later: their KV is gone */
     int            n_finished;
     const int64_t* finished_ids;        /* finished by length after the PREVIOUS plan; their blocks are free again */
+    /* state slots: every sequence that holds blocks also holds one of max_num_seqs slots for per-sequence recurrent
+     * state (convolution tails, matrix states), from its admission until it is released; freed slots are handed out
+     * again, lowest first.  A chunk with prefill_start = 0 must treat its slot's contents as zero. */
+    const int32_t* decode_state_slots;  /* [n_decode] */
+    const int32_t* prefill_state_slots; /* [n_prefill] */
 } b2_step_plan;
 
 B2_API b2_scheduler* b2_sched_create(int64_t num_blocks, int bs, int max_num_seqs, int max_model_len,
@@ -396,6 +401,13 @@ B2_API void    b2_sched_destroy(b2_scheduler* s);
 B2_API int     b2_sched_add_request(b2_scheduler* s, int64_t req_id, int prompt_len, int max_new_tokens);
 B2_API int     b2_sched_finish(b2_scheduler* s, int64_t req_id);                          /* EOS / abort */
 B2_API int     b2_sched_step(b2_scheduler* s, b2_step_plan* plan);
+/* Replay mode: the caller dictates the step instead of the policy above.  Entry i appends counts[i] tokens to request
+ * ids[i]; an unknown id is admitted on the spot (blocks + a state slot; B2_ENOMEM when max_num_seqs sequences are live or
+ * the pool cannot hold the step -- nothing is preempted, and nothing of the step is applied then).  An entry of one token
+ * on a sequence that already holds tokens is planned as a decode row, everything else as a prompt chunk (prefill_last =
+ * 0), rows in entry order within each group.  Requests leave through b2_sched_finish.  Do not mix with b2_sched_step /
+ * b2_sched_add_request on one scheduler. */
+B2_API int     b2_sched_step_explicit(b2_scheduler* s, const int64_t* ids, const int32_t* counts, int n, b2_step_plan* plan);
 B2_API int64_t b2_sched_num_waiting(const b2_scheduler* s);
 B2_API int64_t b2_sched_num_running(const b2_scheduler* s);
 B2_API int64_t b2_sched_num_free_blocks(const b2_scheduler* s);
@@ -451,6 +463,52 @@ B2_API int b2_comm_push_allreduce_rms_norm(void* comm, const void* partial, int6
                                            void* residual, const void* weight, int T, int64_t out_stride,
                                            int64_t res_stride, float eps, void* stream);
 B2_API int b2_comm_allgather_cols(void* comm, const void* local, int64_t local_stride, int T, int cols, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Building blocks of decoders beyond the Llama layer (hyper_norm.cu, delta_rule.cu, chunk_attention.cu, moe.cu).
+ * Every op exists for two activation types: B2_ACT_BF16 (weights, activations and caches in bf16) and B2_ACT_F32
+ * (everything in fp32).  The residual streams, all statistics, softmax, router logits and recurrent state are fp32 in
+ * both.  Small parameter vectors (norm weights, convolution taps, gates' constants, router bias, stream mixing) are
+ * always fp32.  Sequences of a batch are described by cu_q [n+1] (rows), ctx_start [n] (tokens already cached; < 0 marks
+ * a padding row group), block_tables [n, max_nb] and state_slot [n] (< 0: none), all int32 on the device.
+ * The op-by-op semantics are at the top of each source file.
+ * ------------------------------------------------------------------------------------------- */
+#define B2_ACT_BF16   0
+#define B2_ACT_F32    1
+#define B2_NORM_LAYER 0   /* (x - mean) / sqrt(var + eps) * w */
+#define B2_NORM_RMS   1   /* x / sqrt(mean(x^2) + eps) * w */
+B2_API int b2_embed_streams(float* x, const void* embed, int act_dtype, const int64_t* tokens, int T, int D, int S,
+                            float scale, void* stream);
+B2_API int b2_hc_step(float* x, int T, int S, int D, const void* y, int64_t y_stride, const float* mix,
+                      const float* out_w, const float* in_w, const float* norm_w, float eps, int norm_kind, void* h,
+                      int64_t h_stride, int act_dtype, void* stream);
+B2_API int b2_delta_prep(const void* proj, int64_t proj_stride, int off_b, int off_a, int act_dtype, int T, int H,
+                         int G, int dk, int dv, int taps, const float* conv_w, const float* A_log,
+                         const float* dt_bias, const int32_t* cu_q, const int32_t* ctx_start,
+                         const int32_t* state_slot, int n_seq, void* conv_state, float* qkv, float* beta, float* decay,
+                         void* stream);
+B2_API int b2_delta_scan(const float* qkv, const float* beta, const float* decay, int H, int G, int dk, int dv,
+                         const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
+                         float* state, float* o, void* stream);
+B2_API int b2_delta_out(const float* o, const void* proj, int64_t proj_stride, int off_g, int act_dtype, int T, int H,
+                        int dv, const float* norm_w, float eps, void* out, int64_t out_stride, void* stream);
+B2_API int b2_qknorm_cache(const void* qkv, int64_t qkv_stride, int act_dtype, int T, int H, int G, int dk, int dv,
+                           const float* q_w, const float* k_w, float eps, const int64_t* slots, int bs, void* q_out,
+                           void* k_cache, void* v_cache, void* stream);
+B2_API int b2_chunk_attention(void* out, const void* q, const void* k_cache, const void* v_cache, int act_dtype,
+                              const int32_t* block_tables, int max_nb, const int32_t* cu_q, const int32_t* ctx_start,
+                              int n_seq, int T, int H, int G, int dk, int dv, int bs, float scale, int chunk, float sink,
+                              float sink_logit, void* stream);
+B2_API int b2_moe_tile_rows(void);
+B2_API int b2_moe_capacity(int n, int E);
+B2_API int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
+                        int D, int E, int top, int32_t* ids, float* weights, void* stream);
+B2_API int b2_moe_align(const int32_t* ids, int n, int E, int cap, int32_t* sorted, int32_t* tile_expert, int32_t* place,
+                        void* stream);
+B2_API int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gate, const void* w_up, const void* w_down,
+                          int act_dtype, int T, int D, int F, int top, int cap, const int32_t* sorted,
+                          const int32_t* tile_expert, const int32_t* place, const float* weights, void* act, float* rows,
+                          void* y, int64_t y_stride, void* stream);
 
 #ifdef __cplusplus
 }

@@ -11,11 +11,18 @@ import os
 from pathlib import Path
 
 PKG_ROOT = Path(__file__).resolve().parent.parent          # vllm-backend-public_b200/
-LIB_PATH = Path(os.environ.get("B200ATTN_LIB", PKG_ROOT / "lib" / "libb200attn.so"))
+_DEFAULT_LIB_PATH = PKG_ROOT / "lib" / "libb200attn.so"
+LIB_PATH = Path(os.environ.get("B200ATTN_LIB", _DEFAULT_LIB_PATH))
+# `make core`: the host runtime, sampling and the kernels of csrc/Makefile's SRCS_MIX only -- what a model without
+# paged-decode / tcgen05-prefill attention needs.  Used when the full library is not built (a first start compiles
+# this part alone); the entry points it lacks raise B2Error when called.
+CORE_LIB_PATH = PKG_ROOT / "lib" / "libb200core.so"
 
 B2_OK, B2_EINVAL, B2_EUNSUPPORTED, B2_ECUDA, B2_ENOMEM, B2_ENOTFOUND, B2_EEXISTS = 0, -1, -2, -3, -4, -5, -6
 KV_BF16, KV_FP8_E4M3 = 0, 1
-ABI_VERSION = 1
+ABI_VERSION = 2
+ACT_BF16, ACT_F32 = 0, 1
+NORM_LAYER, NORM_RMS = 0, 1
 
 _ERRNAMES = {-1: "B2_EINVAL", -2: "B2_EUNSUPPORTED", -3: "B2_ECUDA", -4: "B2_ENOMEM",
              -5: "B2_ENOTFOUND", -6: "B2_EEXISTS"}
@@ -78,6 +85,7 @@ SIGNATURES = {
     "b2_sched_add_request": (i32, [vp, i64, i32, i32]),
     "b2_sched_finish": (i32, [vp, i64]),
     "b2_sched_step": (i32, [vp, vp]),
+    "b2_sched_step_explicit": (i32, [vp, vp, vp, i32, vp]),
     "b2_sched_num_waiting": (i64, [vp]),
     "b2_sched_num_running": (i64, [vp]),
     "b2_sched_num_free_blocks": (i64, [vp]),
@@ -95,9 +103,30 @@ SIGNATURES = {
     "b2_comm_allreduce_rms_norm": (i32, [vp, i32, vp, vp, vp, i32, i64, i64, f32, vp]),
     "b2_comm_push_allreduce_rms_norm": (i32, [vp, vp, i64, vp, vp, vp, i32, i64, i64, f32, vp]),
     "b2_comm_allgather_cols": (i32, [vp, vp, i64, i32, i32, vp]),
+    "b2_embed_streams": (i32, [vp, vp, i32, vp, i32, i32, i32, f32, vp]),
+    "b2_hc_step": (i32, [vp, i32, i32, i32, vp, i64, vp, vp, vp, vp, f32, i32, vp, i64, i32, vp]),
+    "b2_delta_prep": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp,
+                            vp, vp]),
+    "b2_delta_scan": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, i32, vp, vp, vp]),
+    "b2_delta_out": (i32, [vp, vp, i64, i32, i32, i32, i32, i32, vp, f32, vp, i64, vp]),
+    "b2_qknorm_cache": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, vp, vp, f32, vp, i32, vp, vp, vp, vp]),
+    "b2_chunk_attention": (i32, [vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, f32,
+                                 f32, vp]),
+    "b2_moe_tile_rows": (i32, []),
+    "b2_moe_capacity": (i32, [i32, i32]),
+    "b2_moe_route": (i32, [vp, i64, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
+    "b2_moe_align": (i32, [vp, i32, i32, i32, vp, vp, vp, vp]),
+    "b2_moe_experts": (i32, [vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i64, vp]),
 }
 
 _lib = None
+
+
+def _not_built(name: str, path: Path):
+    def stub(*_a, **_k):
+        raise B2Error(B2_EUNSUPPORTED, f"{name} is not part of {path.name}: build the full library "
+                                       f"(`make -C {PKG_ROOT / 'csrc'}`)")
+    return stub
 
 
 def load() -> C.CDLL:
@@ -105,13 +134,23 @@ def load() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path, partial = LIB_PATH, False
+    if not path.exists() and path == _DEFAULT_LIB_PATH and CORE_LIB_PATH.exists():
+        path, partial = CORE_LIB_PATH, True
+    if not path.exists():
         raise ImportError(
             f"{LIB_PATH} not found: the sm_100a extension is not built. b200attn has no CPU or "
             f"PyTorch fallback; build it with `make -C {PKG_ROOT / 'csrc'}`.")
-    lib = C.CDLL(str(LIB_PATH))
+    lib = C.CDLL(str(path))
+    partial = partial or path.name == CORE_LIB_PATH.name
     for name, (res, args) in SIGNATURES.items():
-        fn = getattr(lib, name)          # AttributeError if the symbol is missing
+        try:
+            fn = getattr(lib, name)      # AttributeError if the symbol is missing
+        except AttributeError:
+            if not partial:
+                raise
+            setattr(lib, name, _not_built(name, path))
+            continue
         fn.restype = res
         fn.argtypes = args
     v = lib.b2_version()

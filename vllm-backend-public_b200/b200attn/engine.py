@@ -1,4 +1,8 @@
-"""Continuous-batching engine: C++ scheduler (b2_sched_*) -> token batch -> LlamaModel.forward -> b2_sample.
+"""Continuous-batching engine: C++ scheduler (b2_sched_*) -> token batch -> model.forward -> b2_sample.
+
+The model is whatever the configuration builds (cfg.build_model): LlamaModel, or a family registered in
+b200attn.model.ARCHITECTURES.  A model owns its paged K/V pools (alloc_cache) and, if it has recurrent layers, one
+state slot per live sequence (alloc_state); the scheduler hands out blocks, cache slots and state slots.
 
 This is the process the reference deploys and probes (reference benchmark-vllm/vllm_manager.py:371-374,
 888-983); its limits are the launch parameters of `VLLMConfig` (reference benchmark-vllm/models.py:8-15):
@@ -24,7 +28,7 @@ import numpy as np
 import torch
 
 from . import ops
-from .model import LlamaModel, ModelConfig, PrefillBatch
+from .model import ModelConfig, PrefillBatch
 from .scheduler import Scheduler, StepPlan
 
 
@@ -72,6 +76,21 @@ class EngineStats:
     mixed_busy_s: float = 0.0
 
 
+def _newest_token(r: "Request") -> int:
+    """The token a decode row writes: the last one sampled, or (replay) the last one fed."""
+    return r.output_ids[-1] if r.output_ids else r.prompt_ids[-1]
+
+
+def _sampleable(logits: torch.Tensor) -> torch.Tensor:
+    """b2_sample reads bf16 rows that start on 16-byte boundaries: fp32 logits are rounded, odd vocabularies padded."""
+    if logits.dtype == torch.bfloat16 and (logits.shape[0] <= 1 or logits.stride(0) % 8 == 0):
+        return logits
+    V = logits.shape[1]
+    buf = torch.empty(logits.shape[0], (V + 7) // 8 * 8, dtype=torch.bfloat16, device=logits.device)
+    buf[:, :V].copy_(logits)
+    return buf[:, :V]
+
+
 def _buckets(max_batch: int) -> List[int]:
     b = [1, 2, 4, 8]
     b += list(range(16, max_batch + 1, 8))
@@ -84,7 +103,7 @@ class LLMEngine:
                  max_model_len: int = 8192, block_size: int = 16, gpu_memory_utilization: float = 0.9,
                  max_num_batched_tokens: int = 8192, num_blocks: Optional[int] = None, seed: int = 0,
                  weights_dir=None, eos_token_id: Optional[int] = None, enforce_eager: bool = False,
-                 kv_cache_dtype: str = "auto", tp=None):
+                 kv_cache_dtype: str = "auto", tp=None, dtype: str = "bfloat16"):
         """`tp`: b200attn.tp.TPGroup when the engine runs tensor-parallel (one engine per rank, all built with the same
         arguments).  Rank 0 owns the request queue and publishes admissions / aborts before every step; the other ranks
         mirror its steps from `worker_loop()`."""
@@ -92,7 +111,13 @@ class LLMEngine:
             raise RuntimeError("b200attn engine needs a CUDA device: there is no CPU path")
         if kv_cache_dtype not in ("auto", "bfloat16", "bf16", "fp8", "fp8_e4m3"):
             raise ValueError(f"kv-cache-dtype {kv_cache_dtype!r}: supported are auto / bfloat16 / fp8 (= fp8_e4m3)")
-        self.kv_dtype = torch.uint8 if kv_cache_dtype.startswith("fp8") else torch.bfloat16
+        if dtype not in ("auto", "bfloat16", "bf16", "float32", "fp32", "float"):
+            raise ValueError(f"dtype {dtype!r}: supported are auto / bfloat16 / float32")
+        self.dtype = torch.float32 if dtype in ("float32", "fp32", "float") else torch.bfloat16
+        self.kv_dtype = torch.uint8 if kv_cache_dtype.startswith("fp8") else self.dtype
+        if self.dtype == torch.float32:               # true fp32 products: no TF32 in the library GEMMs
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
         self.dev = device or torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(self.dev)
         self.tp = tp if tp is not None and tp.size > 1 else None
@@ -110,9 +135,9 @@ class LLMEngine:
 
         # weights first, then size the block pool from what is left (gpu_memory_utilization of the whole device)
         free0, total = torch.cuda.mem_get_info(self.dev)
-        self.model = LlamaModel(cfg, self.dev, num_blocks=1, block_size=block_size, seed=seed, weights_dir=weights_dir,
-                                max_position=self.max_model_len, kv_dtype=self.kv_dtype, tp=self.tp)
-        del self.model.kv
+        self.model = cfg.build_model(self.dev, num_blocks=1, block_size=block_size, seed=seed, weights_dir=weights_dir,
+                                     max_position=self.max_model_len, kv_dtype=self.kv_dtype, tp=self.tp,
+                                     dtype=self.dtype, max_num_seqs=max_num_seqs)
         if self.tp is not None:
             # peer-mapped exchange buffers (csrc/comm.cu): partial sums of up to max(max_num_seqs, 256) rows take the
             # one-shot path; the gathered logits hold one row per sequence
@@ -123,10 +148,10 @@ class LLMEngine:
             torch.cuda.synchronize(self.dev)
             free1, _ = torch.cuda.mem_get_info(self.dev)
             used = total - free1
-            act = self.max_num_batched_tokens * (3 * cfg.inter + self.model.qkv_width + 6 * cfg.hidden) * 2 \
-                + max_num_seqs * cfg.vocab * 2 * 2 + (1 << 30)
-            budget = int(total * util) - used - act
-            per_block = cfg.kv_bytes_per_token(1 if self.kv_dtype == torch.uint8 else 2, self.tp_size) * block_size
+            elem = 1 if self.kv_dtype == torch.uint8 else (4 if self.kv_dtype == torch.float32 else 2)
+            act = cfg.activation_bytes(self.max_num_batched_tokens, max_num_seqs)
+            budget = int(total * util) - used - act - max_num_seqs * cfg.state_bytes_per_seq(elem)
+            per_block = max(cfg.kv_bytes_per_token(elem, self.tp_size) * block_size, 1)
             want = max_num_seqs * self.max_nb + 64                   # every sequence at max_model_len
             num_blocks = max(min(budget // per_block, want), 0)
             if self.tp is not None:
@@ -140,9 +165,8 @@ class LLMEngine:
             raise RuntimeError(f"KV pool of {num_blocks} blocks cannot hold one sequence of max_model_len "
                                f"{self.max_model_len} ({self.max_nb + 1} blocks of {block_size} tokens needed)")
         self.num_blocks = int(num_blocks)
-        self.model.num_blocks = self.num_blocks
-        self.model.kv = torch.zeros(cfg.layers, 2, self.num_blocks, self.model.Hkv, block_size, cfg.d,
-                                    dtype=self.kv_dtype, device=self.dev)
+        self.model.alloc_cache(self.num_blocks)
+        self.model.alloc_state(max_num_seqs)
         self.sched = Scheduler(self.num_blocks, block_size, max_num_seqs, self.max_model_len, self.max_num_batched_tokens)
 
         # pinned staging + static device inputs of the decode graph
@@ -152,6 +176,8 @@ class LLMEngine:
         self._h_bt = torch.zeros(B, self.max_nb, dtype=torch.int32).pin_memory()
         self._h_temp = torch.zeros(2 * B, dtype=torch.float32).pin_memory()       # temperature | top_p
         self._h_topk = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self._h_state = torch.zeros(B, dtype=torch.int32).pin_memory()            # state slot of every decode row
+        self._d_state = torch.zeros(B, dtype=torch.int32, device=self.dev)
         self._h_out = torch.zeros(max(B, 1), dtype=torch.int64).pin_memory()
         self._d_i64 = torch.zeros(3 * B, dtype=torch.int64, device=self.dev)
         self._d_i32 = torch.zeros(2 * B, dtype=torch.int32, device=self.dev)
@@ -170,9 +196,9 @@ class LLMEngine:
         self.time_device = False                 # bench: CUDA events around every decode replay -> stats.device_ms
         self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         self.model.prepare_decode(B, self.max_nb)     # workspace sized once for max_num_seqs + per-layer decode plans
-        self._launches_per_layer = 7          # rms, rope+cache, attention(+merge), rms, silu, (GEMMs are cuBLAS)
-        # what the decode-schedule planner sees: this rank's heads
-        self._plan_heads = (self.model.Hq, self.model.Hkv)
+        self._launches_per_layer = self.model.launches_per_layer
+        self._graph_logits: Dict[Tuple[int, int], torch.Tensor] = {}   # a decode graph's logits, rewritten by every replay
+        self._replay: Dict[object, Request] = {}                      # replay_step: caller's key -> request
 
         self.requests: Dict[int, Request] = {}
         self._ids = itertools.count(1)
@@ -269,7 +295,7 @@ class LLMEngine:
         pin = lambda n, dt: torch.zeros(n, dtype=dt).pin_memory()                      # noqa: E731
         self._hm_tok, self._hm_slot, self._hm_pos = pin(Tm, torch.int64), pin(Tm, torch.int64), pin(Tm, torch.int32)
         self._hm_aux = pin(2 * B, torch.int64)                 # seeds [B] | sample rows [B]
-        self._hm_meta = pin(3 * B + 1, torch.int32)            # decode seq_lens [B] | cu_q [B + 1] | ctx_start [B]
+        self._hm_meta = pin(5 * B + 1, torch.int32)            # decode seq_lens [B] | cu_q [B + 1] | ctx_start [B] | state slots: decode [B], chunks [B]
         self._hm_temp = pin(2 * B, torch.float32)             # temperature [B] | top_p [B]
         self._hm_topk = pin(B, torch.int32)
         self._hm_pbt = torch.zeros(B, self.max_nb, dtype=torch.int32).pin_memory()
@@ -344,9 +370,11 @@ class LLMEngine:
 
         def run():
             logits = self.model.forward(self._d_i64[:bucket], self._d_i32[:bucket], self._d_i64[B:B + bucket], bucket,
-                                        self._d_bt[:bucket], self._d_i32[B:B + bucket], None, None, num_splits)
-            ops.sample(logits, self._d_temp[:bucket], self._d_i64[2 * B:2 * B + bucket], out=self._d_out[:bucket],
-                       top_k=self._d_topk[:bucket], top_p=self._d_temp[B:B + bucket])
+                                        self._d_bt[:bucket], self._d_i32[B:B + bucket], None, None, num_splits,
+                                        dec_state_slots=self._d_state[:bucket])
+            self._graph_logits[key] = logits
+            ops.sample(_sampleable(logits), self._d_temp[:bucket], self._d_i64[2 * B:2 * B + bucket],
+                       out=self._d_out[:bucket], top_k=self._d_topk[:bucket], top_p=self._d_temp[B:B + bucket])
 
         if not self.use_graphs:
             self._graphs[key] = run
@@ -365,14 +393,15 @@ class LLMEngine:
         self._graphs[key] = g.replay
         return g.replay
 
-    def _run_decode(self, plan: StepPlan):
+    def _run_decode(self, plan: StepPlan, want_rows: Optional[List[int]] = None):
+        """Decode-only step.  `want_rows` (replay): return the fp32 logits of those batch rows instead of tokens."""
         nd, B = len(plan.decode_ids), self.max_num_seqs
         bucket = next(b for b in self._buckets if b >= nd)
         reqs = [self.requests[int(i)] for i in plan.decode_ids]
         i64, i32 = self._np_i64, self._np_i32
         sl = plan.seq_lens
         i64[:bucket] = 0
-        i64[:nd] = [r.output_ids[-1] for r in reqs]
+        i64[:nd] = [_newest_token(r) for r in reqs]
         i64[B:B + bucket] = -1
         i64[B:B + nd] = plan.slot_mapping
         i64[2 * B:2 * B + nd] = [self._step_seed(r) for r in reqs]
@@ -388,10 +417,12 @@ class LLMEngine:
         self._np_temp[B:B + nd] = [r.params.top_p for r in reqs]
         self._np_topk[:bucket] = 0
         self._np_topk[:nd] = [r.params.top_k for r in reqs]
-        num_splits = ops.plan_num_splits(self._h_i32[B:B + nd], *self._plan_heads, self.cfg.d, self.block_size,
-                                         ops.KV_FP8_E4M3 if self.kv_dtype == torch.uint8 else ops.KV_BF16)
+        self._h_state.numpy()[:bucket] = 0
+        self._h_state.numpy()[:nd] = plan.decode_state_slots
+        num_splits = self.model.decode_schedule(self._h_i32[B:B + nd])
         replay = self._decode_graph(bucket, num_splits)
         with torch.cuda.stream(self._stream):
+            self._d_state.copy_(self._h_state, non_blocking=True)
             self._d_i64.copy_(self._h_i64, non_blocking=True)
             self._d_i32.copy_(self._h_i32, non_blocking=True)
             self._d_bt[:nd, :used].copy_(self._h_bt[:nd, :used], non_blocking=True)
@@ -403,6 +434,10 @@ class LLMEngine:
             if self.time_device:
                 self._ev[1].record(self._stream)
             self._h_out[:bucket].copy_(self._d_out[:bucket], non_blocking=True)
+            wanted = None
+            if want_rows is not None:
+                rows = torch.tensor(want_rows, dtype=torch.int64, device=self.dev)
+                wanted = self._graph_logits[(bucket, num_splits)].index_select(0, rows).float().cpu()
         tw = time.perf_counter()
         self._stream.synchronize()
         self.stats.sync_wait_s += time.perf_counter() - tw
@@ -410,23 +445,29 @@ class LLMEngine:
             self.stats.device_ms += self._ev[0].elapsed_time(self._ev[1])
             self.stats.device_steps += 1
         self.stats.gpu_launches += self.cfg.layers * self._launches_per_layer + 3
+        if want_rows is not None:
+            return wanted
         return reqs, self._h_out[:nd].tolist()
 
     # ------------------------------------------------------------------------------------ step with prompt chunks
-    def _run_mixed(self, plan: StepPlan):
+    def _run_mixed(self, plan: StepPlan, want_rows: Optional[List[int]] = None):
+        """Step with prompt chunks.  `want_rows` (replay): return the fp32 logits of those batch rows instead of tokens."""
         self._ensure_mixed_buffers()
         nd, npf, B = len(plan.decode_ids), len(plan.prefill_ids), self.max_num_seqs
         Tp = int(plan.prefill_len.sum())
         T = nd + Tp
         tok, slot, pos = self._hm_tok.numpy(), self._hm_slot.numpy(), self._hm_pos.numpy()
-        aux, meta = self._hm_aux.numpy(), self._hm_meta.numpy()
+        aux_t = self._hm_aux
+        aux, meta = aux_t.numpy(), self._hm_meta.numpy()
         dreqs = [self.requests[int(i)] for i in plan.decode_ids]
         preqs = [self.requests[int(i)] for i in plan.prefill_ids]
         if nd:
-            tok[:nd] = [r.output_ids[-1] for r in dreqs]
+            tok[:nd] = [_newest_token(r) for r in dreqs]
             slot[:nd] = plan.slot_mapping
             pos[:nd] = plan.seq_lens - 1
             meta[:nd] = plan.seq_lens
+            meta[3 * B + 1:3 * B + 1 + nd] = plan.decode_state_slots
+        meta[4 * B + 1:4 * B + 1 + npf] = plan.prefill_state_slots
         slot[nd:T] = plan.prefill_slots
         cu, ctx = meta[B:B + npf + 1], meta[2 * B + 1:2 * B + 1 + npf]
         cu[0] = 0
@@ -445,14 +486,21 @@ class LLMEngine:
                 rows.append(off - 1)
             if st == 0 and r.n_preempted == 0:
                 self.stats.prompt_tokens += len(r.prompt_ids)
+        if want_rows is not None:
+            rows = list(want_rows)
+            if len(rows) > B:                # more logits rows than sampling rows: a buffer of their own
+                aux_t = torch.zeros(B + len(rows), dtype=torch.int64)
+                aux = aux_t.numpy()
+            sample_reqs = []
         ns = len(rows)
-        aux[:ns] = [self._step_seed(r) for r in sample_reqs]
+        aux[:len(sample_reqs)] = [self._step_seed(r) for r in sample_reqs]
         aux[B:B + ns] = rows
         if ns == 0:
             aux[B] = 0                       # no row to sample this step: lm_head runs on one dummy row
-        self._hm_temp.numpy()[:ns] = [r.params.temperature for r in sample_reqs]
-        self._hm_temp.numpy()[B:B + ns] = [r.params.top_p for r in sample_reqs]
-        self._hm_topk.numpy()[:ns] = [r.params.top_k for r in sample_reqs]
+        nsr = len(sample_reqs)
+        self._hm_temp.numpy()[:nsr] = [r.params.temperature for r in sample_reqs]
+        self._hm_temp.numpy()[B:B + nsr] = [r.params.top_p for r in sample_reqs]
+        self._hm_topk.numpy()[:nsr] = [r.params.top_k for r in sample_reqs]
         bsz = self.block_size
         used_p = (int((plan.prefill_start + plan.prefill_len).max()) + bsz - 1) // bsz
         self._hm_pbt.numpy()[:npf, :used_p] = plan.prefill_block_tables[:, :used_p]
@@ -460,14 +508,13 @@ class LLMEngine:
         if nd:
             used = (int(plan.seq_lens.max()) + bsz - 1) // bsz
             self._np_bt[:nd, :used] = plan.block_tables[:, :used]
-            num_splits = ops.plan_num_splits(self._hm_meta[:nd], *self._plan_heads, self.cfg.d, bsz,
-                                                 ops.KV_FP8_E4M3 if self.kv_dtype == torch.uint8 else ops.KV_BF16)
+            num_splits = self.model.decode_schedule(self._hm_meta[:nd])
         dev = self.dev
         with torch.cuda.stream(self._stream):
             d_tok = self._hm_tok[:T].to(dev, non_blocking=True)
             d_slot = self._hm_slot[:T].to(dev, non_blocking=True)
             d_pos = self._hm_pos[:T].to(dev, non_blocking=True)
-            d_aux = self._hm_aux.to(dev, non_blocking=True)
+            d_aux = aux_t.to(dev, non_blocking=True)
             d_meta = self._hm_meta.to(dev, non_blocking=True)
             d_temp = self._hm_temp.to(dev, non_blocking=True)
             d_topk = self._hm_topk.to(dev, non_blocking=True)
@@ -478,16 +525,82 @@ class LLMEngine:
                 dec_bt, dec_sl = self._d_bt[:nd], d_meta[:nd]
             pf = PrefillBatch(cu_q=d_meta[B:B + npf + 1], ctx_start=d_meta[2 * B + 1:2 * B + 1 + npf],
                               block_tables=d_pbt, total_tokens=Tp,
-                              kv_lens_host=(plan.prefill_start + plan.prefill_len).tolist())
-            logits = self.model.forward(d_tok, d_pos, d_slot, nd, dec_bt, dec_sl, pf, d_aux[B:B + max(ns, 1)], num_splits)
-            if ns:
+                              kv_lens_host=(plan.prefill_start + plan.prefill_len).tolist(),
+                              state_slots=d_meta[4 * B + 1:4 * B + 1 + npf])
+            logits = self.model.forward(d_tok, d_pos, d_slot, nd, dec_bt, dec_sl, pf, d_aux[B:B + max(ns, 1)], num_splits,
+                                        dec_state_slots=d_meta[3 * B + 1:3 * B + 1 + nd])
+            if want_rows is not None:
+                wanted = logits[:ns].float().cpu()
+            elif ns:
+                logits = _sampleable(logits)
                 out = ops.sample(logits, d_temp[:ns], d_aux[:ns], top_k=d_topk[:ns], top_p=d_temp[B:B + ns])
                 self._h_out[:ns].copy_(out, non_blocking=True)
         tw = time.perf_counter()
         self._stream.synchronize()
         self.stats.sync_wait_s += time.perf_counter() - tw
         self.stats.gpu_launches += self.cfg.layers * (self._launches_per_layer + 1) + 3
+        if want_rows is not None:
+            return wanted
         return sample_reqs, (self._h_out[:ns].tolist() if ns else [])
+
+    # ------------------------------------------------------------------------------------ replaying a given schedule
+    def replay_step(self, entries, end=()) -> torch.Tensor:
+        """Run one step that the caller dictates instead of the scheduling policy, and return logits instead of
+        sampling.  entries: [(key, tokens, want)] -- request `key` (any hashable; admitted at its first entry) is fed its
+        next `tokens`; `want` lists the places among them whose logits are returned.  end: keys whose blocks and state
+        slot are released after the step.  All entries run as ONE batch through the same scheduler structures, pools,
+        state slots and kernels as generation (b2_sched_step_explicit: one-token entries of known sequences are decode
+        rows -- a decode-only step replays the CUDA graph --, the rest prompt chunks).  Returns fp32 CPU logits
+        [sum(len(want)), vocab] in entry order.  Do not mix with add_request / step on one engine."""
+        if self.tp is not None:
+            raise RuntimeError("replay_step runs on a single-GPU engine")
+        plan_ids, counts = [], []
+        if sum(len(t) for _, t, _ in entries) > self.max_num_batched_tokens:
+            raise ValueError(f"the step brings more than max_num_batched_tokens = {self.max_num_batched_tokens} tokens")
+        for key, toks, want in entries:
+            if not toks or any(not 0 <= int(t) < self.cfg.vocab for t in toks):
+                raise ValueError(f"request {key!r}: empty entry or token id outside the vocabulary [0, {self.cfg.vocab})")
+            if any(not 0 <= int(k) < len(toks) for k in want):
+                raise ValueError(f"request {key!r}: wanted place outside its {len(toks)} tokens")
+            r = self._replay.get(key)
+            if r is None:
+                r = Request(next(self._ids), [], SamplingParams(max_tokens=1, temperature=0.0), t_arrival=time.perf_counter())
+                self._replay[key] = r
+                self.requests[r.id] = r
+            plan_ids.append(r.id)
+            counts.append(len(toks))
+        try:
+            plan = self.sched.step_explicit(plan_ids, counts)
+        except Exception:
+            for key, _, _ in entries:                        # nothing of the step was applied: forget the newcomers
+                r = self._replay.get(key)
+                if r is not None and not r.prompt_ids:
+                    self.requests.pop(r.id, None)
+                    del self._replay[key]
+            raise
+        first_row = {int(rid): i for i, rid in enumerate(plan.decode_ids)}
+        off = len(plan.decode_ids)
+        for rid, n in zip(plan.prefill_ids, plan.prefill_len):
+            first_row[int(rid)] = off
+            off += int(n)
+        want_rows = []
+        for key, toks, want in entries:
+            r = self._replay[key]
+            r.prompt_ids.extend(int(t) for t in toks)
+            want_rows += [first_row[r.id] + int(k) for k in want]
+        if len(plan.prefill_ids) == 0:
+            logits = self._run_decode(plan, want_rows=want_rows)
+            self.stats.decode_steps += 1
+        else:
+            logits = self._run_mixed(plan, want_rows=want_rows)
+            self.stats.mixed_steps += 1
+        self.stats.steps += 1
+        for key in end:
+            r = self._replay.pop(key, None)
+            if r is not None:
+                self.sched.finish(r.id)
+                self.requests.pop(r.id, None)
+        return logits
 
     def capture_all(self) -> int:
         """Capture the decode graph of every (batch bucket, schedule) now instead of at first use (server start-up).

@@ -51,6 +51,16 @@ class ModelConfig:
     def kv_bytes_per_token(self, kv_elem_bytes: int = 2, tp: int = 1) -> int:
         return 2 * self.layers * (self.Hkv // tp) * self.d * kv_elem_bytes
 
+    def state_bytes_per_seq(self, elem_bytes: int = 2) -> int:
+        return 0                                     # attention only: nothing is kept per sequence besides K/V
+
+    def activation_bytes(self, tokens: int, seqs: int, elem_bytes: int = 2) -> int:
+        qkv_width = (self.Hq + 2 * self.Hkv) * self.d
+        return tokens * (3 * self.inter + qkv_width + 6 * self.hidden) * 2 + seqs * self.vocab * 2 * 2 + (1 << 30)
+
+    def build_model(self, device, **kw):
+        return LlamaModel(self, device, **kw)
+
 
 _LLAMA3_SCALING = dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
 
@@ -93,11 +103,22 @@ def config_from_hf_dir(path: Path) -> ModelConfig:
         max_position=int(c.get("max_position_embeddings", 8192)))
 
 
-def resolve_config(model: str) -> ModelConfig:
-    """`--model` of the launch contract -> geometry.  A local HF directory wins; else the registry (by short name or
-    by the hub id the reference's configs use); unknown names fail loudly (nothing can be downloaded here)."""
+# config.json `architecture` -> loader of that model family's configuration (families register themselves below)
+ARCHITECTURES: Dict[str, object] = {}
+
+
+def resolve_config(model: str):
+    """`--model` of the launch contract -> geometry.  A local directory wins: its config.json names the model family
+    by `architecture` (ARCHITECTURES), anything else is read as a Hugging Face Llama / Qwen2 config; else the registry
+    (by short name or by the hub id the reference's configs use); unknown names fail loudly (nothing can be downloaded
+    here).  Every configuration class offers build_model(device, **engine arguments)."""
     p = Path(model)
     if p.is_dir() and (p / "config.json").exists():
+        arch = json.loads((p / "config.json").read_text()).get("architecture")
+        if arch in ARCHITECTURES:
+            return ARCHITECTURES[arch](p)
+        if arch is not None:
+            raise ValueError(f"{model}: unknown architecture {arch!r} (known: {sorted(ARCHITECTURES)})")
         return config_from_hf_dir(p)
     key = model.lower()
     key = _ALIASES.get(key, key)
@@ -131,6 +152,7 @@ class PrefillBatch:
     block_tables: torch.Tensor    # int32 [n, max_nb]
     total_tokens: int
     kv_lens_host: Optional[list] = None   # [ctx_start[c] + len_c] as host ints (fp8 cache: sizes the bf16 scratch)
+    state_slots: Optional[torch.Tensor] = None   # int32 [n]: per-sequence state slot (models with recurrent state)
 
 
 class LlamaModel:
@@ -138,12 +160,15 @@ class LlamaModel:
 
     def __init__(self, cfg: ModelConfig, device: torch.device, num_blocks: int, block_size: int = 16,
                  seed: int = 0, weights_dir: Optional[Path] = None, max_position: Optional[int] = None,
-                 kv_dtype: torch.dtype = torch.bfloat16, tp=None):
+                 kv_dtype: torch.dtype = torch.bfloat16, tp=None, dtype: torch.dtype = torch.bfloat16,
+                 max_num_seqs: int = 1):
         """`tp`: a b200attn.tp.TPGroup (or None).  With tp.size > 1 this instance holds rank tp.rank's shard: q / kv
         heads and MLP columns split over the ranks (column-parallel wqkv / wgu, row-parallel wo / wdown), the
         lm_head split over the vocabulary, embedding and norms replicated; the KV pool holds Hkv / tp heads."""
         if cfg.d != 128:
             raise ValueError(f"head_dim {cfg.d}: the attention kernels are built for 128")
+        if dtype != torch.bfloat16:
+            raise ValueError(f"dtype {dtype}: the Llama path is bf16 only")
         if device.type != "cuda":
             raise ValueError("LlamaModel needs a CUDA device (b200attn has no CPU path)")
         self.cfg, self.dev, self.bs, self.num_blocks = cfg, device, block_size, num_blocks
@@ -163,8 +188,8 @@ class LlamaModel:
         else:
             self._random_init(seed)
         self.cos_sin = rope_table(self.max_position, cfg.d, cfg.rope_theta, cfg.rope_scaling, device)
-        # KV pool: [layers, 2, num_blocks, Hkv, bs, d]; one (block, head) tile = bs x d contiguous ("HND")
-        self.kv = torch.zeros(cfg.layers, 2, num_blocks, self.Hkv, block_size, cfg.d, dtype=kv_dtype, device=device)
+        self._kv_dtype = kv_dtype
+        self.alloc_cache(num_blocks)
         self.k_scale = self.v_scale = None
         if kv_dtype != torch.bfloat16:
             self.k_scale = torch.ones(1, dtype=torch.float32, device=device)
@@ -231,6 +256,24 @@ class LlamaModel:
         put("norm", get("model.norm.weight"))
         put("lm_head", self.w["embed"] if c.tie_embeddings or "lm_head.weight" not in raw else get("lm_head.weight"))
 
+    supports_fp32 = False
+    launches_per_layer = 7          # rms, rope+cache, attention(+merge), rms, silu, (GEMMs are cuBLAS)
+
+    def alloc_cache(self, num_blocks: int) -> None:
+        """KV pool: [layers, 2, num_blocks, Hkv, bs, d]; one (block, head) tile = bs x d contiguous ("HND")."""
+        self.num_blocks = int(num_blocks)
+        self.kv = None
+        self.kv = torch.zeros(self.cfg.layers, 2, self.num_blocks, self.Hkv, self.bs, self.cfg.d, dtype=self._kv_dtype,
+                              device=self.dev)
+
+    def alloc_state(self, max_num_seqs: int) -> None:
+        """Nothing is kept per sequence besides K/V."""
+
+    def decode_schedule(self, seq_lens_host: torch.Tensor) -> int:
+        """Schedule of the paged-decode kernel for this step (b2_paged_decode_plan_splits)."""
+        return ops.plan_num_splits(seq_lens_host, self.Hq, self.Hkv, self.cfg.d, self.bs,
+                                   ops.KV_FP8_E4M3 if self._kv_dtype == torch.uint8 else ops.KV_BF16)
+
     def weight_bytes(self) -> int:
         seen, n = set(), 0
         for t in self.w.values():
@@ -262,7 +305,8 @@ class LlamaModel:
 
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, n_decode: int,
                 dec_block_tables: Optional[torch.Tensor], dec_seq_lens: Optional[torch.Tensor],
-                prefill: Optional[PrefillBatch], sample_rows: Optional[torch.Tensor], num_splits: int = 0) -> torch.Tensor:
+                prefill: Optional[PrefillBatch], sample_rows: Optional[torch.Tensor], num_splits: int = 0,
+                dec_state_slots: Optional[torch.Tensor] = None) -> torch.Tensor:
         """tokens int64 [T] (rows [0, n_decode) = one new token per running sequence, the rest = prompt chunks),
         positions int32 [T], slots int64 [T].  Returns bf16 logits [len(sample_rows) or T, vocab]."""
         c, w = self.cfg, self.w
@@ -358,3 +402,11 @@ class LlamaModel:
             return self.tp.allreduce_rms_norm(slot, part.shape[0], weight, resid, self.cfg.eps)
         self.tp.all_reduce_nccl(part)
         return ops.rms_norm(part, weight, self.cfg.eps, residual=resid, out=part)
+
+
+def _register_families() -> None:
+    from . import kofadra
+    ARCHITECTURES[kofadra.ARCHITECTURE] = kofadra.config_from_dir
+
+
+_register_families()

@@ -631,3 +631,242 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, see
     _lib.check(lib.b2_sample_filtered(_ptr(out), _ptr(logits), B, V, st, _ptr(temperature), _ptr(seeds), _ptr(top_k),
                                       _ptr(top_p), _stream(dev)))
     return out
+
+
+# ======================================================================================================================
+# Building blocks beyond the Llama layer (csrc/hyper_norm.cu, delta_rule.cu, chunk_attention.cu, moe.cu).
+# Activations / weights / caches are bf16 or fp32 (one type per call); residual streams, statistics and recurrent state
+# are fp32 in both.  Small parameter vectors are fp32.
+# ======================================================================================================================
+from dataclasses import dataclass  # noqa: E402
+
+from ._lib import ACT_BF16, ACT_F32, NORM_LAYER, NORM_RMS  # noqa: E402,F401
+
+
+def _act(t: torch.Tensor, name: str) -> int:
+    if t.dtype == torch.bfloat16:
+        return ACT_BF16
+    if t.dtype == torch.float32:
+        return ACT_F32
+    raise ValueError(f"{name} must be bf16 or fp32, not {t.dtype}")
+
+
+def _f32(t: Optional[torch.Tensor], name: str, shape=None) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or not t.is_contiguous() or (shape is not None and tuple(t.shape) != tuple(shape)):
+        raise ValueError(f"{name} must be a contiguous fp32 tensor" + (f" of shape {tuple(shape)}" if shape else ""))
+    return t
+
+
+def _mat(t: torch.Tensor, name: str):
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError(f"{name} must be [rows, cols] with a contiguous last axis")
+    return t.shape[0], t.shape[1], (t.stride(0) if t.shape[0] > 1 else t.shape[1])
+
+
+@dataclass
+class SeqBatch:
+    """The sequences of one step, as every varlen op of this section reads them (all int32, on the device).
+    Sequence i owns batch rows cu_q[i] .. cu_q[i+1]-1 and has ctx_start[i] tokens in the cache before them; a negative
+    ctx_start marks padding rows (CUDA-graph buckets).  A decode row is a sequence with one row."""
+    cu_q: torch.Tensor                       # [n + 1]
+    ctx_start: torch.Tensor                  # [n]
+    block_tables: Optional[torch.Tensor]     # [n, max_nb]
+    state_slots: Optional[torch.Tensor]      # [n]; < 0: the sequence keeps no recurrent state
+    n_seq: int
+    rows: int
+
+
+def embed_streams(embed: torch.Tensor, tokens: torch.Tensor, streams: int, scale: float) -> torch.Tensor:
+    """x[t, s, :] = embed[tokens[t]] * scale for s < streams: fp32 [T, streams, D]  (b2_embed_streams)."""
+    lib = _lib.load()
+    dev = _need_cuda(embed=embed, tokens=tokens)
+    if tokens.dtype != torch.int64 or not tokens.is_contiguous() or not embed.is_contiguous():
+        raise ValueError("tokens must be contiguous int64, embed contiguous")
+    T, D = tokens.shape[0], embed.shape[1]
+    x = torch.empty(T, streams, D, dtype=torch.float32, device=dev)
+    _lib.check(lib.b2_embed_streams(_ptr(x), _ptr(embed), _act(embed, "embed"), _ptr(tokens), T, D, streams, float(scale),
+                                    _stream(dev)))
+    return x
+
+
+def hc_step(x: torch.Tensor, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+            out_w: Optional[torch.Tensor] = None, in_w: Optional[torch.Tensor] = None,
+            norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6, norm_kind: int = NORM_LAYER,
+            h_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """One pass over the fp32 residual streams x [T, S, D] (updated in place):
+    with y [T, D]:      x[:, j] <- sum_s mix[s, j] * x[:, s] + out_w[j] * y      (mix / out_w None = identity / ones)
+    with norm_w [D]:    returns h = norm(sum_s in_w[s] * x[:, s]) * norm_w as h_dtype (in_w None = ones).
+    S = 1 with the defaults is residual add + norm.  b2_hc_step."""
+    lib = _lib.load()
+    dev = _need_cuda(x=x, y=y, mix=mix, out_w=out_w, in_w=in_w, norm_w=norm_w)
+    if x.dtype != torch.float32 or x.dim() != 3 or not x.is_contiguous():
+        raise ValueError("x must be contiguous fp32 [T, S, D]")
+    T, S, D = x.shape
+    ys = 0
+    if y is not None:
+        Ty, Dy, ys = _mat(y, "y")
+        if (Ty, Dy) != (T, D):
+            raise ValueError("y must be [T, D]")
+    _f32(mix, "mix", (S, S)), _f32(out_w, "out_w", (S,)), _f32(in_w, "in_w", (S,)), _f32(norm_w, "norm_w", (D,))
+    h = None
+    if norm_w is not None:
+        h_dtype = h_dtype or (y.dtype if y is not None else torch.bfloat16)
+        h = torch.empty(T, D, dtype=h_dtype, device=dev)
+    act = _act(h if h is not None else y, "h / y") if (h is not None or y is not None) else ACT_BF16
+    if h is not None and y is not None and h.dtype != y.dtype:
+        raise ValueError("h_dtype must equal y's dtype")
+    _lib.check(lib.b2_hc_step(_ptr(x), T, S, D, _ptr(y), ys, _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(norm_w), float(eps),
+                              norm_kind, _ptr(h), D, act, _stream(dev)))
+    return h
+
+
+def delta_prep(proj: torch.Tensor, off_b: int, off_a: int, H: int, G: int, dk: int, dv: int, taps: int,
+               conv_w: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, batch: SeqBatch,
+               conv_state: Optional[torch.Tensor]):
+    """Inputs of the gated delta-rule scan from the fused projection rows proj [T, >= 2*G*dk + H*dv + ...] whose first
+    columns are q | k | v; off_b / off_a are the columns of the two per-head gate inputs.  conv_state
+    [slots, taps-1, C] (proj's dtype) is read for the chunk's first tokens and then advanced.  Returns fp32
+    qkv [T, C] (q, k unit vectors, q times dk^-1/2), beta [T, H], decay [T, H].  b2_delta_prep."""
+    lib = _lib.load()
+    dev = _need_cuda(proj=proj, conv_w=conv_w, A_log=A_log, dt_bias=dt_bias, conv_state=conv_state)
+    T, P, ps = _mat(proj, "proj")
+    C = 2 * G * dk + H * dv
+    if P < C or not 0 <= off_b <= P - H or not 0 <= off_a <= P - H:
+        raise ValueError("proj is narrower than its column map")
+    _f32(conv_w, "conv_w", (C, taps)), _f32(A_log, "A_log", (H,)), _f32(dt_bias, "dt_bias", (H,))
+    if taps > 1:
+        if conv_state is None or conv_state.dtype != proj.dtype or not conv_state.is_contiguous() \
+                or tuple(conv_state.shape[1:]) != (taps - 1, C):
+            raise ValueError(f"conv_state must be contiguous [slots, {taps - 1}, {C}] of proj's dtype")
+    qkv = torch.empty(T, C, dtype=torch.float32, device=dev)
+    beta = torch.empty(T, H, dtype=torch.float32, device=dev)
+    decay = torch.empty(T, H, dtype=torch.float32, device=dev)
+    _lib.check(lib.b2_delta_prep(_ptr(proj), ps, off_b, off_a, _act(proj, "proj"), T, H, G, dk, dv, taps, _ptr(conv_w),
+                                 _ptr(A_log), _ptr(dt_bias), _ptr(batch.cu_q), _ptr(batch.ctx_start),
+                                 _ptr(batch.state_slots), batch.n_seq, _ptr(conv_state), _ptr(qkv), _ptr(beta),
+                                 _ptr(decay), _stream(dev)))
+    return qkv, beta, decay
+
+
+def delta_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, H: int, G: int, dk: int, dv: int,
+               batch: SeqBatch, state: torch.Tensor) -> torch.Tensor:
+    """Per (sequence, head), token after token: S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+    state fp32 [slots, H, dk, dv] is read when the sequence has context and written back.  Returns o fp32 [T, H, dv]."""
+    lib = _lib.load()
+    dev = _need_cuda(qkv=qkv, beta=beta, decay=decay, state=state)
+    T = qkv.shape[0]
+    _f32(qkv, "qkv", (T, 2 * G * dk + H * dv)), _f32(beta, "beta", (T, H)), _f32(decay, "decay", (T, H))
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, dk, dv):
+        raise ValueError(f"state must be contiguous fp32 [slots, {H}, {dk}, {dv}]")
+    o = torch.empty(T, H, dv, dtype=torch.float32, device=dev)
+    _lib.check(lib.b2_delta_scan(_ptr(qkv), _ptr(beta), _ptr(decay), H, G, dk, dv, _ptr(batch.cu_q), _ptr(batch.ctx_start),
+                                 _ptr(batch.state_slots), batch.n_seq, _ptr(state), _ptr(o), _stream(dev)))
+    return o
+
+
+def delta_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, norm_w: torch.Tensor, eps: float) -> torch.Tensor:
+    """o / rms(o over dv) * norm_w * silu(proj[:, off_g + h*dv + i]) -> [T, H*dv] of proj's dtype.  b2_delta_out."""
+    lib = _lib.load()
+    dev = _need_cuda(o=o, proj=proj, norm_w=norm_w)
+    T, H, dv = o.shape
+    _f32(o, "o"), _f32(norm_w, "norm_w", (dv,))
+    _, P, ps = _mat(proj, "proj")
+    if off_g + H * dv > P:
+        raise ValueError("gate columns outside proj")
+    out = torch.empty(T, H * dv, dtype=proj.dtype, device=dev)
+    _lib.check(lib.b2_delta_out(_ptr(o), _ptr(proj), ps, off_g, _act(proj, "proj"), T, H, dv, _ptr(norm_w), float(eps),
+                                _ptr(out), H * dv, _stream(dev)))
+    return out
+
+
+def qknorm_cache(qkv: torch.Tensor, H: int, G: int, dk: int, dv: int, q_w: Optional[torch.Tensor],
+                 k_w: Optional[torch.Tensor], eps: float, slots: torch.Tensor, k_cache: torch.Tensor,
+                 v_cache: torch.Tensor) -> torch.Tensor:
+    """Rows qkv [T, H*dk + G*dk + G*dv]: q and k heads are RMS-normalised over dk (times q_w / k_w), k and v go to the
+    paged pools k_cache [nb, G, bs, dk] / v_cache [nb, G, bs, dv] at slots[t] (< 0 skips).  Returns q [T, H, dk]."""
+    lib = _lib.load()
+    dev = _need_cuda(qkv=qkv, q_w=q_w, k_w=k_w, slots=slots, k_cache=k_cache, v_cache=v_cache)
+    T, P, ps = _mat(qkv, "qkv")
+    if P != H * dk + G * dk + G * dv:
+        raise ValueError("qkv width differs from H*dk + G*dk + G*dv")
+    _f32(q_w, "q_w", (dk,)), _f32(k_w, "k_w", (dk,))
+    nb, bs = k_cache.shape[0], k_cache.shape[2]
+    if tuple(k_cache.shape) != (nb, G, bs, dk) or tuple(v_cache.shape) != (nb, G, bs, dv) or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous() or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+        raise ValueError("k_cache / v_cache must be contiguous [nb, G, bs, dk] / [nb, G, bs, dv] of qkv's dtype")
+    if slots.dtype != torch.int64 or slots.shape != (T,) or not slots.is_contiguous():
+        raise ValueError("slots must be contiguous int64 [T]")
+    q = torch.empty(T, H, dk, dtype=qkv.dtype, device=dev)
+    _lib.check(lib.b2_qknorm_cache(_ptr(qkv), ps, _act(qkv, "qkv"), T, H, G, dk, dv, _ptr(q_w), _ptr(k_w), float(eps),
+                                   _ptr(slots), bs, _ptr(q), _ptr(k_cache), _ptr(v_cache), _stream(dev)))
+    return q
+
+
+def chunk_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: SeqBatch, scale: float,
+                    chunk: int = 0, sink: float = 0.0, sink_logit: float = 0.0) -> torch.Tensor:
+    """Attention of q [T, H, dk] over the paged pools.  Row at position p sees positions j <= p with
+    j // chunk == p // chunk (chunk = 0: all j <= p); the denominator carries sink * exp(sink_logit).
+    Returns [T, H, dv] of q's dtype.  b2_chunk_attention."""
+    lib = _lib.load()
+    dev = _need_cuda(q=q, k_cache=k_cache, v_cache=v_cache)
+    T, H, dk = q.shape
+    nb, G, bs, dv = v_cache.shape
+    if not q.is_contiguous() or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or tuple(k_cache.shape) != (nb, G, bs, dk):
+        raise ValueError("q must be contiguous and the pools of its dtype, k_cache [nb, G, bs, dk]")
+    bt = batch.block_tables
+    if bt is None or bt.dtype != torch.int32 or bt.dim() != 2 or bt.stride(1) != 1 or bt.shape[0] < batch.n_seq \
+            or (bt.shape[0] > 1 and bt.stride(0) != bt.shape[1]):
+        raise ValueError("block_tables must be a contiguous int32 [n_seq, max_nb]")
+    out = torch.empty(T, H, dv, dtype=q.dtype, device=dev)
+    _lib.check(lib.b2_chunk_attention(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _act(q, "q"), _ptr(bt), bt.shape[1],
+                                      _ptr(batch.cu_q), _ptr(batch.ctx_start), batch.n_seq, T, H, G, dk, dv, bs,
+                                      float(scale), int(chunk), float(sink), float(sink_logit), _stream(dev)))
+    return out
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """ids int32 [T, top], weights fp32 [T, top]: the top logits of h W_r^T + bias (fp32), softmax over the chosen."""
+    lib = _lib.load()
+    dev = _need_cuda(h=h, w_router=w_router, bias=bias)
+    T, D, hs = _mat(h, "h")
+    E = w_router.shape[0]
+    if w_router.dtype != h.dtype or tuple(w_router.shape) != (E, D) or not w_router.is_contiguous():
+        raise ValueError("w_router must be contiguous [E, D] of h's dtype")
+    _f32(bias, "bias", (E,))
+    ids = torch.empty(T, top, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, top, dtype=torch.float32, device=dev)
+    _lib.check(lib.b2_moe_route(_ptr(h), hs, _ptr(w_router), _ptr(bias), _act(h, "h"), T, D, E, top, _ptr(ids), _ptr(wts),
+                                _stream(dev)))
+    return ids, wts
+
+
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                w_down: torch.Tensor) -> torch.Tensor:
+    """y[t] = sum_j wts[t, j] * W_down[e] (silu(W_gate[e] h[t]) * (W_up[e] h[t])), e = ids[t, j].
+    w_gate, w_up [E, F, D]; w_down [E, D, F].  Sorting by expert, both grouped products and the weighted sum run on the
+    device without a host read (b2_moe_align, b2_moe_experts)."""
+    lib = _lib.load()
+    dev = _need_cuda(h=h, ids=ids, wts=wts, w_gate=w_gate, w_up=w_up, w_down=w_down)
+    T, D, hs = _mat(h, "h")
+    E, F, _ = w_gate.shape
+    top = ids.shape[1]
+    for name, w, shape in (("w_gate", w_gate, (E, F, D)), ("w_up", w_up, (E, F, D)), ("w_down", w_down, (E, D, F))):
+        if w.dtype != h.dtype or tuple(w.shape) != shape or not w.is_contiguous():
+            raise ValueError(f"{name} must be contiguous {shape} of h's dtype")
+    if ids.dtype != torch.int32 or not ids.is_contiguous() or tuple(ids.shape) != (T, top):
+        raise ValueError("ids must be contiguous int32 [T, top]")
+    _f32(wts, "wts", (T, top))
+    n = T * top
+    cap = lib.b2_moe_capacity(n, E)
+    meta = torch.empty(cap + cap // lib.b2_moe_tile_rows() + n, dtype=torch.int32, device=dev)
+    srt, tile_e, place = meta[:cap], meta[cap:cap + cap // lib.b2_moe_tile_rows()], meta[cap + cap // lib.b2_moe_tile_rows():]
+    _lib.check(lib.b2_moe_align(_ptr(ids), n, E, cap, _ptr(srt), _ptr(tile_e), _ptr(place), _stream(dev)))
+    act = torch.empty(cap, F, dtype=h.dtype, device=dev)
+    rows = torch.empty(cap, D, dtype=torch.float32, device=dev)
+    y = torch.empty(T, D, dtype=h.dtype, device=dev)
+    _lib.check(lib.b2_moe_experts(_ptr(h), hs, _ptr(w_gate), _ptr(w_up), _ptr(w_down), _act(h, "h"), T, D, F, top, cap,
+                                  _ptr(srt), _ptr(tile_e), _ptr(place), _ptr(wts), _ptr(act), _ptr(rows), _ptr(y), D,
+                                  _stream(dev)))
+    return y

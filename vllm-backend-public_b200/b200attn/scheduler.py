@@ -25,6 +25,7 @@ class _Plan(C.Structure):
         ("prefill_slots", C.POINTER(C.c_int64)), ("prefill_block_tables", C.POINTER(C.c_int32)),
         ("n_preempted", C.c_int), ("preempted_ids", C.POINTER(C.c_int64)),
         ("n_finished", C.c_int), ("finished_ids", C.POINTER(C.c_int64)),
+        ("decode_state_slots", C.POINTER(C.c_int32)), ("prefill_state_slots", C.POINTER(C.c_int32)),
     ]
 
 
@@ -48,6 +49,8 @@ class StepPlan:
     prefill_block_tables: np.ndarray  # [n_prefill, max_nb] int32
     preempted_ids: np.ndarray
     finished_ids: np.ndarray
+    decode_state_slots: np.ndarray = None    # [n_decode] int32: the sequence's slot for recurrent state
+    prefill_state_slots: np.ndarray = None   # [n_prefill] int32
 
     @property
     def empty(self) -> bool:
@@ -101,6 +104,20 @@ class Scheduler:
     def step(self) -> StepPlan:
         p = self._plan
         _lib.check(self._lib.b2_sched_step(self._h, C.byref(p)))
+        return self._view(p)
+
+    def step_explicit(self, ids, counts) -> StepPlan:
+        """Replay mode (b2_sched_step_explicit): entry i appends counts[i] tokens to request ids[i]; unknown ids are
+        admitted.  One-token entries on sequences that hold tokens become decode rows, the rest prompt chunks."""
+        ids = np.ascontiguousarray(ids, dtype=np.int64)
+        counts = np.ascontiguousarray(counts, dtype=np.int32)
+        p = self._plan
+        _lib.check(self._lib.b2_sched_step_explicit(self._h, ids.ctypes.data_as(C.c_void_p),
+                                                    counts.ctypes.data_as(C.c_void_p), len(ids), C.byref(p)))
+        return self._view(p)
+
+    @staticmethod
+    def _view(p: _Plan) -> StepPlan:
         nd, npf, nb = p.n_decode, p.n_prefill, p.max_nb
         return StepPlan(
             decode_ids=_arr(p.decode_ids, nd, np.int64),
@@ -115,4 +132,6 @@ class Scheduler:
             prefill_block_tables=_arr(p.prefill_block_tables, npf * nb, np.int32).reshape(npf, nb),
             preempted_ids=_arr(p.preempted_ids, p.n_preempted, np.int64),
             finished_ids=_arr(p.finished_ids, p.n_finished, np.int64),
+            decode_state_slots=_arr(p.decode_state_slots, nd, np.int32),
+            prefill_state_slots=_arr(p.prefill_state_slots, npf, np.int32),
         )

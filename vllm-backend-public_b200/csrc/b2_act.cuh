@@ -1,0 +1,62 @@
+// b2_act.cuh -- element access for kernels that are instantiated for two activation types:
+// __nv_bfloat16 (serving) and float (the all-32-bit mode).  Math is always fp32; only loads and stores differ.
+#pragma once
+#include "b2_common.cuh"
+
+#ifdef __CUDACC__
+namespace b2 {
+
+__device__ __forceinline__ float ld(const float* p) { return *p; }
+__device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void st(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over the block; `red` is 33 floats of shared memory.  Every thread gets the result.  May be called repeatedly.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                      // protects `red` against the previous call's readers
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// Sequence of batch row `row` when rows are grouped by cu[0..n] (cu[0] = 0, cu[n] = rows in the batch).
+__device__ __forceinline__ int seq_of_row(const int32_t* cu, int n, int row) {
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (cu[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+}  // namespace b2
+#endif
+
+// activation type selector of the C ABI
+#define B2_DISPATCH_ACT(act_dtype, T, ...)                                  \
+    do {                                                                    \
+        if ((act_dtype) == B2_ACT_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else { using T = float; __VA_ARGS__; }                              \
+    } while (0)

@@ -1,0 +1,272 @@
+// delta_rule.cu -- a gated delta-rule recurrent mixer over a varlen token batch with per-sequence state slots.
+//
+// One fused projection gives, per token, the row  [ q (G*dk) | k (G*dk) | v (H*dv) | ... ]  and three more column
+// ranges for the gate inputs (b: H, a: H) and the output gate (H*dv).  The mixer then runs
+//
+//   b2_delta_prep          short causal depthwise convolution (taps) + SiLU over the q|k|v channels, reading the
+//                          taps-1 inputs before the chunk from the sequence's state slot; q and k made unit vectors per
+//                          head (q also times dk^-1/2); beta = sigmoid(b); decay = exp(-exp(A_log) * softplus(a + dt_bias)).
+//                          All of it in fp32, written as fp32 rows for the scan.
+//   b2_delta_conv_state    the slot's convolution tail becomes the last taps-1 inputs of the sequence.
+//   b2_delta_scan          per (sequence, head): S <- decay*S;  u = beta*(v - S^T k);  S <- S + k u^T;  o = S^T q,
+//                          token after token, S [dk, dv] fp32 held in registers for the whole chunk and loaded from /
+//                          stored to the slot once.  A one-token chunk is the decode step: one read and one write of
+//                          the state, which is its HBM roofline.
+//   b2_delta_out           o / rms(o over dv) * w  * SiLU(output gate)  -> activation type, ready for the out projection.
+//
+// A batch is n sequences; sequence i owns rows cu_q[i] .. cu_q[i+1]-1, has ctx_start[i] tokens before them (< 0: the row
+// group is padding and is skipped) and keeps its state in slot state_slot[i] (< 0: no state is read or written).  A
+// sequence with ctx_start = 0 starts from a zero state whatever the slot holds, so slots need no clearing on reuse.
+#include "b2_act.cuh"
+
+namespace {
+
+constexpr int kMaxTaps = 16;
+
+// ------------------------------------------------------------------------------------------------- prep
+template <typename T>
+__global__ void delta_prep_kernel(const T* __restrict__ proj, int64_t proj_stride, int off_b, int off_a,
+                                  int H, int G, int dk, int dv, int taps, const float* __restrict__ conv_w,
+                                  const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                  const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start,
+                                  const int32_t* __restrict__ state_slot, int n_seq, const T* __restrict__ conv_state,
+                                  float* __restrict__ qkv, float* __restrict__ beta, float* __restrict__ decay) {
+    extern __shared__ float ch[];                    // [C] conv + SiLU outputs of this token
+    const int row = blockIdx.x;
+    const int C = 2 * G * dk + H * dv;
+    const int seq = b2::seq_of_row(cu_q, n_seq, row);
+    const int li = row - cu_q[seq];
+    const int ctx = ctx_start[seq];
+    if (ctx < 0) return;
+    const int slot = state_slot[seq];
+    const T* st = (slot >= 0 && ctx > 0) ? conv_state + (size_t)slot * (taps - 1) * C : nullptr;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {             // input at position ctx + li - j times the tap taps-1-j
+            const int l = li - j;
+            float xin = 0.f;
+            if (l >= 0) xin = b2::ld(proj + (size_t)(row - j) * proj_stride + c);
+            else if (ctx + l >= 0 && st) xin = b2::ld(st + (size_t)(l + taps - 1) * C + c);
+            acc = fmaf(conv_w[(size_t)c * taps + (taps - 1 - j)], xin, acc);
+        }
+        ch[c] = b2::silu_f(acc);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float* out = qkv + (size_t)row * C;
+    const float qs = rsqrtf((float)dk);
+    for (int g = wid; g < 2 * G; g += nw) {          // q heads then k heads: unit vectors
+        const float* v = ch + (size_t)g * dk;
+        float ss = 0.f;
+        for (int i = lane; i < dk; i += 32) ss = fmaf(v[i], v[i], ss);
+        ss = b2::warp_sum(ss);
+        const float sc = rsqrtf(ss + 1e-6f) * (g < G ? qs : 1.f);
+        for (int i = lane; i < dk; i += 32) out[(size_t)g * dk + i] = v[i] * sc;
+    }
+    for (int c = 2 * G * dk + threadIdx.x; c < C; c += blockDim.x) out[c] = ch[c];
+    const T* pr = proj + (size_t)row * proj_stride;
+    for (int hh = threadIdx.x; hh < H; hh += blockDim.x) {
+        beta[(size_t)row * H + hh] = b2::sigmoid_f(b2::ld(pr + off_b + hh));
+        decay[(size_t)row * H + hh] = expf(-expf(A_log[hh]) * b2::softplus_f(b2::ld(pr + off_a + hh) + dt_bias[hh]));
+    }
+}
+
+template <typename T>
+__global__ void delta_conv_state_kernel(const T* __restrict__ proj, int64_t proj_stride, int C, int taps,
+                                        const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start,
+                                        const int32_t* __restrict__ state_slot, T* __restrict__ conv_state) {
+    const int seq = blockIdx.x;
+    const int ctx = ctx_start[seq], slot = state_slot[seq];
+    if (ctx < 0 || slot < 0) return;
+    const int r0 = cu_q[seq], n = cu_q[seq + 1] - r0;
+    T* st = conv_state + (size_t)slot * (taps - 1) * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float win[kMaxTaps];
+#pragma unroll
+        for (int i = 0; i < kMaxTaps; ++i) {
+            if (i < taps - 1) {
+                const int l = n - (taps - 1) + i;    // chunk-local index of the input that lands in tail place i
+                float v = 0.f;
+                if (l >= 0) v = b2::ld(proj + (size_t)(r0 + l) * proj_stride + c);
+                else if (ctx + l >= 0 && ctx > 0) v = b2::ld(st + (size_t)(l + taps - 1) * C + c);
+                win[i] = v;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxTaps; ++i)
+            if (i < taps - 1) b2::st(st + (size_t)i * C + c, win[i]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------- scan
+// One warp owns 8 columns of S; a column's dk rows are spread over 4 lanes (rows r, r+4, r+8, ...), NR rows a lane.
+// lane = r * 8 + jj.  The two dot products of a token reduce over the 4 lanes of a column with two shuffles.
+template <int NR>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
+                  int H, int G, int dk, int dv, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start,
+                  const int32_t* __restrict__ state_slot, float* __restrict__ state, float* __restrict__ o) {
+    const int seq = blockIdx.x, hh = blockIdx.y;
+    const int ctx = ctx_start[seq];
+    if (ctx < 0) return;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int r = lane >> 3, jj = lane & 7;
+    const int j = (blockIdx.z * 4 + wid) * 8 + jj;   // column of S
+    const bool col_ok = j < dv;
+    const int slot = state_slot[seq];
+    const int C = 2 * G * dk + H * dv;
+    const int kvh = hh / (H / G);
+    const int r0 = cu_q[seq], n = cu_q[seq + 1] - r0;
+    float S[NR];
+    float* sp = slot >= 0 ? state + ((size_t)slot * H + hh) * dk * dv : nullptr;
+#pragma unroll
+    for (int m = 0; m < NR; ++m) {
+        const int i = r + 4 * m;
+        S[m] = (sp && ctx > 0 && col_ok && i < dk) ? sp[(size_t)i * dv + j] : 0.f;
+    }
+    const float* qrow = qkv + (size_t)r0 * C + (size_t)kvh * dk;
+    const float* krow = qrow + (size_t)G * dk;
+    const float* vrow = qkv + (size_t)r0 * C + (size_t)2 * G * dk + (size_t)hh * dv;
+    const float* vcol = vrow + (col_ok ? j : 0);
+    const float* grow = decay + (size_t)r0 * H + hh;
+    const float* brow = beta + (size_t)r0 * H + hh;
+    float* ocol = o + ((size_t)r0 * H + hh) * dv + (col_ok ? j : 0);
+    // inputs of token t (they do not depend on S: the next token's are fetched while this one's chain runs)
+    auto load = [&](int t, float (&k)[NR], float (&q)[NR], float& g, float& be, float& v) {
+#pragma unroll
+        for (int m = 0; m < NR; ++m) {
+            const int i = r + 4 * m;
+            k[m] = i < dk ? krow[(size_t)t * C + i] : 0.f;
+            q[m] = i < dk ? qrow[(size_t)t * C + i] : 0.f;
+        }
+        g = grow[(size_t)t * H];
+        be = brow[(size_t)t * H];
+        v = col_ok ? vcol[(size_t)t * C] : 0.f;
+    };
+    auto step = [&](int t, const float (&k)[NR], const float (&q)[NR], float g, float be, float v) {
+        float pred = 0.f;
+#pragma unroll
+        for (int m = 0; m < NR; ++m) pred = fmaf(S[m], k[m], pred);
+        pred += __shfl_xor_sync(0xffffffffu, pred, 8);
+        pred += __shfl_xor_sync(0xffffffffu, pred, 16);
+        const float u = be * (v - g * pred);
+        float acc = 0.f;
+#pragma unroll
+        for (int m = 0; m < NR; ++m) {
+            S[m] = fmaf(k[m], u, g * S[m]);
+            acc = fmaf(S[m], q[m], acc);
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+        if (r == 0 && col_ok) ocol[(size_t)t * H * dv] = acc;
+    };
+    float ka[NR], qa[NR], ga, ba, va;
+    if (NR <= 32) {
+        float kb[NR], qb[NR], gb, bb, vb;
+        if (n > 0) load(0, ka, qa, ga, ba, va);
+        for (int t = 0; t < n; t += 2) {
+            if (t + 1 < n) load(t + 1, kb, qb, gb, bb, vb);
+            step(t, ka, qa, ga, ba, va);
+            if (t + 1 < n) {
+                if (t + 2 < n) load(t + 2, ka, qa, ga, ba, va);
+                step(t + 1, kb, qb, gb, bb, vb);
+            }
+        }
+    } else {
+        for (int t = 0; t < n; ++t) {
+            load(t, ka, qa, ga, ba, va);
+            step(t, ka, qa, ga, ba, va);
+        }
+    }
+    if (sp && col_ok) {
+#pragma unroll
+        for (int m = 0; m < NR; ++m) {
+            const int i = r + 4 * m;
+            if (i < dk) sp[(size_t)i * dv + j] = S[m];
+        }
+    }
+}
+
+template <typename T>
+__global__ void delta_out_kernel(const float* __restrict__ o, const T* __restrict__ proj, int64_t proj_stride, int off_g,
+                                 int H, int dv, const float* __restrict__ norm_w, float eps, T* __restrict__ out,
+                                 int64_t out_stride, int rows) {
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);    // (row, head)
+    if (item >= rows * H) return;
+    const int row = item / H, hh = item % H;
+    const float* ov = o + (size_t)item * dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) ss = fmaf(ov[i], ov[i], ss);
+    const float inv = rsqrtf(b2::warp_sum(ss) / (float)dv + eps);
+    const T* gate = proj + (size_t)row * proj_stride + off_g + (size_t)hh * dv;
+    T* dst = out + (size_t)row * out_stride + (size_t)hh * dv;
+    for (int i = lane; i < dv; i += 32) b2::st(dst + i, ov[i] * inv * norm_w[i] * b2::silu_f(b2::ld(gate + i)));
+}
+
+}  // namespace
+
+extern "C" int b2_delta_prep(const void* proj, int64_t proj_stride, int off_b, int off_a, int act_dtype, int T, int H,
+                             int G, int dk, int dv, int taps, const float* conv_w, const float* A_log,
+                             const float* dt_bias, const int32_t* cu_q, const int32_t* ctx_start,
+                             const int32_t* state_slot, int n_seq, void* conv_state, float* qkv, float* beta, float* decay,
+                             void* stream) {
+    B2_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && taps >= 1 && taps <= kMaxTaps, B2_EINVAL,
+               "delta_prep: bad sizes H=%d G=%d dk=%d dv=%d taps=%d", H, G, dk, dv, taps);
+    if (T == 0 || n_seq == 0) return B2_OK;
+    B2_REQUIRE(proj && conv_w && A_log && dt_bias && cu_q && ctx_start && state_slot && qkv && beta && decay, B2_EINVAL,
+               "delta_prep: null pointer");
+    B2_REQUIRE(conv_state || taps == 1, B2_EINVAL, "delta_prep: a convolution of %d taps needs its state", taps);
+    const int C = 2 * G * dk + H * dv;
+    const size_t smem = (size_t)C * sizeof(float);
+    B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "delta_prep: %d channels do not fit shared memory", C);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        auto kern = delta_prep_kernel<A>;
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<T, 256, smem, st>>>(static_cast<const A*>(proj), proj_stride, off_b, off_a, H, G, dk, dv, taps, conv_w, A_log,
+                                   dt_bias, cu_q, ctx_start, state_slot, n_seq, static_cast<const A*>(conv_state), qkv,
+                                   beta, decay);
+    });
+    B2_CUDA_OK(cudaGetLastError());
+    if (taps > 1) {
+        const int by = (C + 255) / 256;
+        B2_DISPATCH_ACT(act_dtype, A, (delta_conv_state_kernel<A><<<dim3(n_seq, by), 256, 0, st>>>(
+            static_cast<const A*>(proj), proj_stride, C, taps, cu_q, ctx_start, state_slot, static_cast<A*>(conv_state))));
+        B2_CUDA_OK(cudaGetLastError());
+    }
+    return B2_OK;
+}
+
+extern "C" int b2_delta_scan(const float* qkv, const float* beta, const float* decay, int H, int G, int dk, int dv,
+                             const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
+                             float* state, float* o, void* stream) {
+    B2_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, B2_EINVAL, "delta_scan: bad sizes");
+    B2_REQUIRE(dk <= 256, B2_EUNSUPPORTED, "delta_scan: key size %d above 256", dk);
+    if (n_seq == 0) return B2_OK;
+    B2_REQUIRE(qkv && beta && decay && cu_q && ctx_start && state_slot && state && o, B2_EINVAL, "delta_scan: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 grid(n_seq, H, (dv + 31) / 32);
+#define B2_SCAN(NR) delta_scan_kernel<NR><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o)
+    if (dk <= 32) B2_SCAN(8);
+    else if (dk <= 64) B2_SCAN(16);
+    else if (dk <= 128) B2_SCAN(32);
+    else B2_SCAN(64);
+#undef B2_SCAN
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_delta_out(const float* o, const void* proj, int64_t proj_stride, int off_g, int act_dtype, int T, int H,
+                            int dv, const float* norm_w, float eps, void* out, int64_t out_stride, void* stream) {
+    B2_REQUIRE(T >= 0 && H > 0 && dv > 0, B2_EINVAL, "delta_out: bad sizes");
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(o && proj && norm_w && out, B2_EINVAL, "delta_out: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int items = T * H, blocks = (items + 7) / 8;
+    B2_DISPATCH_ACT(act_dtype, A, (delta_out_kernel<A><<<blocks, 256, 0, st>>>(o, static_cast<const A*>(proj), proj_stride, off_g,
+                                                                              H, dv, norm_w, eps, static_cast<A*>(out),
+                                                                              out_stride, T)));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}

@@ -1,0 +1,349 @@
+// moe.cu -- a routed mixture of gated feed-forward experts over a token batch.
+//
+//   b2_moe_route     z = W_r h + b in fp32 (one warp per token), the `top` largest logits (lowest index wins a tie), weights =
+//                    softmax over the chosen logits only.
+//   b2_moe_align     counting sort of the T*top (token, choice) pairs by expert into row tiles of kMoeBM rows: every tile
+//                    belongs to one expert, experts are padded to a tile boundary with -1.  Entirely on the device (no host
+//                    read of the counts), so the step stays capturable in a CUDA graph and never waits for the GPU.
+//   b2_moe_gate_up   per tile: act = SiLU(h W_gate[e]^T) * (h W_up[e]^T), rows gathered through the sorted list.
+//   b2_moe_down      per tile: rows = act W_down[e]^T, fp32.
+//   b2_moe_combine   y[t] = sum_j weight[t, j] * rows[place of (t, j)], summed in choice order in fp32: a token's result
+//                    does not depend on what else is in the batch.
+// The two grouped products are tiled through shared memory; bf16 runs on the tensor cores (16x16x16 fragments, fp32
+// accumulation), the all-32-bit mode on fp32 FMAs.  Expert weights are stacked: w_gate, w_up [E, F, D]; w_down [E, D, F].
+#include "b2_act.cuh"
+
+#include <mma.h>
+#include <type_traits>
+
+namespace {
+
+constexpr int kMoeBM = 32, kMoeBN = 64, kMoeBK = 32;
+
+// ------------------------------------------------------------------------------------------------- router
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_r,
+                                 const float* __restrict__ bias, int rows, int D, int E, int top,
+                                 int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float z_sm[];                  // [warps, E]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + wid;
+    if (t >= rows) return;
+    float* z = z_sm + (size_t)wid * E;
+    const T* x = h + (size_t)t * h_stride;
+    for (int e = 0; e < E; ++e) {
+        const T* w = w_r + (size_t)e * D;
+        float a = 0.f;
+        for (int i = lane; i < D; i += 32) a = fmaf(b2::ld(x + i), b2::ld(w + i), a);
+        a = b2::warp_sum(a);
+        if (lane == 0) z[e] = a + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    float v0 = 0.f, sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (z[e] > best) { best = z[e]; arg = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = 0;              // every logit is NaN or -inf: still a valid expert id
+        if (j == 0) v0 = best;
+        const float p = expf(best - v0);
+        sum += p;
+        if (lane == 0) {
+            ids[(size_t)t * top + j] = arg;
+            wts[(size_t)t * top + j] = p;
+            z[arg] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    const float inv = 1.f / sum;
+    for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= inv;
+}
+
+// ------------------------------------------------------------------------------------------------- align
+__global__ void moe_align_kernel(const int32_t* __restrict__ ids, int n, int E, int cap, int32_t* __restrict__ sorted,
+                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ place) {
+    extern __shared__ int sm[];                      // counts [E] | offs [E] | fill [E]
+    int* counts = sm;
+    int* offs = sm + E;
+    int* fill = sm + 2 * E;
+    __shared__ int total;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = fill[e] = 0;
+    for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            offs[e] = run;
+            run += (counts[e] + kMoeBM - 1) / kMoeBM * kMoeBM;
+        }
+        total = run;
+    }
+    __syncthreads();
+    const int tiles = cap / kMoeBM;
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+        for (int t = offs[e] / kMoeBM; t < (offs[e] + counts[e] + kMoeBM - 1) / kMoeBM; ++t) tile_expert[t] = e;
+    for (int t = total / kMoeBM + threadIdx.x; t < tiles; t += blockDim.x) tile_expert[t] = -1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E) {
+            const int p = offs[e] + atomicAdd(&fill[e], 1);
+            sorted[p] = i;
+            place[i] = p;
+        } else {
+            place[i] = -1;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------- grouped products
+template <typename T> struct Pad { static constexpr int v = 8; };
+template <> struct Pad<float> { static constexpr int v = 1; };
+
+// dst[r][0..BK) = row r of a [nrows, K] operand at columns k0.., zero outside; rowptr(r) = nullptr for a padding row
+template <typename T, int NROWS, typename F>
+__device__ __forceinline__ void load_tile(T* dst, F rowptr, int k0, int K, bool vec) {
+    constexpr int LD = kMoeBK + Pad<T>::v;
+    constexpr int VE = 16 / sizeof(T);
+    if (vec) {
+        for (int idx = threadIdx.x; idx < NROWS * (kMoeBK / VE); idx += blockDim.x) {
+            const int r = idx / (kMoeBK / VE), kv = (idx % (kMoeBK / VE)) * VE;
+            const T* p = rowptr(r);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (p && k0 + kv < K) v = *reinterpret_cast<const uint4*>(p + k0 + kv);
+            if constexpr (std::is_same<T, float>::value) {
+                float* d = reinterpret_cast<float*>(dst) + r * LD + kv;
+                d[0] = __uint_as_float(v.x); d[1] = __uint_as_float(v.y); d[2] = __uint_as_float(v.z); d[3] = __uint_as_float(v.w);
+            } else {
+                *reinterpret_cast<uint4*>(dst + r * LD + kv) = v;
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < NROWS * kMoeBK; idx += blockDim.x) {
+            const int r = idx / kMoeBK, kk = idx % kMoeBK;
+            const T* p = rowptr(r);
+            T v = T(0.f);
+            if (p && k0 + kk < K) v = p[k0 + kk];
+            dst[r * LD + kk] = v;
+        }
+    }
+}
+
+// C[BM, BN] (+)= A[BM, K] B[BN, K]^T for NB B operands that share A (NB = 2: gate and up).  Result in c_sm[NB][BM][BN].
+template <typename T, int NB, typename FA, typename FB0, typename FB1>
+__device__ __forceinline__ void tile_product(FA a_row, FB0 b0_row, FB1 b1_row, int K, bool vec, T* a_sm, T* b_sm, float* c_sm) {
+    constexpr int LD = kMoeBK + Pad<T>::v;
+    const int tid = threadIdx.x;
+    if constexpr (std::is_same<T, float>::value) {
+        const int ty = tid >> 4, tx = tid & 15;      // rows ty*4 .. +3, columns tx + 16 c
+        float acc[NB][4][4];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[b][i][c] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += kMoeBK) {
+            __syncthreads();
+            load_tile<T, kMoeBM>(a_sm, a_row, k0, K, vec);
+            load_tile<T, kMoeBN>(b_sm, b0_row, k0, K, vec);
+            if (NB == 2) load_tile<T, kMoeBN>(b_sm + kMoeBN * LD, b1_row, k0, K, vec);
+            __syncthreads();
+#pragma unroll 8
+            for (int kk = 0; kk < kMoeBK; ++kk) {
+                float a[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = a_sm[(ty * 4 + i) * LD + kk];
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float bv = b_sm[(b * kMoeBN + tx + 16 * c) * LD + kk];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[b][i][c] = fmaf(a[i], bv, acc[b][i][c]);
+                    }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) c_sm[(b * kMoeBM + ty * 4 + i) * kMoeBN + tx + 16 * c] = acc[b][i][c];
+    } else {
+        using namespace nvcuda;
+        const int wid = tid >> 5;
+        const int wm = wid >> 1, wn = wid & 1;       // warp tile: rows wm*16 .. +15, columns wn*32 .. +31
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[NB][2];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) wmma::fill_fragment(acc[b][c], 0.f);
+        for (int k0 = 0; k0 < K; k0 += kMoeBK) {
+            __syncthreads();
+            load_tile<T, kMoeBM>(a_sm, a_row, k0, K, vec);
+            load_tile<T, kMoeBN>(b_sm, b0_row, k0, K, vec);
+            if (NB == 2) load_tile<T, kMoeBN>(b_sm + kMoeBN * LD, b1_row, k0, K, vec);
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < kMoeBK; kk += 16) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+                wmma::load_matrix_sync(fa, a_sm + (wm * 16) * LD + kk, LD);
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
+                        wmma::load_matrix_sync(fb, b_sm + (b * kMoeBN + wn * 32 + c * 16) * LD + kk, LD);
+                        wmma::mma_sync(acc[b][c], fa, fb, acc[b][c]);
+                    }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+                wmma::store_matrix_sync(c_sm + (b * kMoeBM + wm * 16) * kMoeBN + wn * 32 + c * 16, acc[b][c], kMoeBN,
+                                        wmma::mem_row_major);
+    }
+    __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_gate, const T* __restrict__ w_up,
+                   const int32_t* __restrict__ sorted, const int32_t* __restrict__ tile_expert, int top, int D, int F,
+                   bool vec, T* __restrict__ act) {
+    constexpr int LD = kMoeBK + Pad<T>::v;
+    __shared__ __align__(32) T a_sm[kMoeBM * LD];
+    __shared__ __align__(32) T b_sm[2 * kMoeBN * LD];
+    __shared__ __align__(32) float c_sm[2 * kMoeBM * kMoeBN];
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int m0 = blockIdx.x * kMoeBM, n0 = blockIdx.y * kMoeBN;
+    const T* wg = w_gate + (size_t)e * F * D;
+    const T* wu = w_up + (size_t)e * F * D;
+    auto a_row = [&](int r) -> const T* {
+        const int s = sorted[m0 + r];
+        return s >= 0 ? h + (size_t)(s / top) * h_stride : nullptr;
+    };
+    auto g_row = [&](int r) -> const T* { return n0 + r < F ? wg + (size_t)(n0 + r) * D : nullptr; };
+    auto u_row = [&](int r) -> const T* { return n0 + r < F ? wu + (size_t)(n0 + r) * D : nullptr; };
+    tile_product<T, 2>(a_row, g_row, u_row, D, vec, a_sm, b_sm, c_sm);
+    for (int idx = threadIdx.x; idx < kMoeBM * kMoeBN; idx += blockDim.x) {
+        const int r = idx / kMoeBN, c = idx % kMoeBN;
+        if (n0 + c < F && sorted[m0 + r] >= 0) {
+            const float g = c_sm[idx], u = c_sm[kMoeBM * kMoeBN + idx];
+            b2::st(act + (size_t)(m0 + r) * F + n0 + c, b2::silu_f(g) * u);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int32_t* __restrict__ sorted,
+                const int32_t* __restrict__ tile_expert, int D, int F, bool vec, float* __restrict__ rows) {
+    constexpr int LD = kMoeBK + Pad<T>::v;
+    __shared__ __align__(32) T a_sm[kMoeBM * LD];
+    __shared__ __align__(32) T b_sm[kMoeBN * LD];
+    __shared__ __align__(32) float c_sm[kMoeBM * kMoeBN];
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int m0 = blockIdx.x * kMoeBM, n0 = blockIdx.y * kMoeBN;
+    const T* wd = w_down + (size_t)e * D * F;
+    auto a_row = [&](int r) -> const T* { return sorted[m0 + r] >= 0 ? act + (size_t)(m0 + r) * F : nullptr; };
+    auto d_row = [&](int r) -> const T* { return n0 + r < D ? wd + (size_t)(n0 + r) * F : nullptr; };
+    tile_product<T, 1>(a_row, d_row, d_row, F, vec, a_sm, b_sm, c_sm);
+    for (int idx = threadIdx.x; idx < kMoeBM * kMoeBN; idx += blockDim.x) {
+        const int r = idx / kMoeBN, c = idx % kMoeBN;
+        if (n0 + c < D && sorted[m0 + r] >= 0) rows[(size_t)(m0 + r) * D + n0 + c] = c_sm[idx];
+    }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ place,
+                                   const float* __restrict__ wts, int top, int D, T* __restrict__ y, int64_t y_stride) {
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float a = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int p = place[(size_t)t * top + j];
+            if (p >= 0) a = fmaf(wts[(size_t)t * top + j], rows[(size_t)p * D + d], a);
+        }
+        b2::st(y + (size_t)t * y_stride + d, a);
+    }
+}
+
+}  // namespace
+
+extern "C" int b2_moe_tile_rows(void) { return kMoeBM; }
+
+// rows of the sorted list for n (token, choice) pairs over E experts: every expert that is used pads to a tile boundary
+extern "C" int b2_moe_capacity(int n, int E) {
+    const int used = n < E ? n : E;
+    return (n + used * (kMoeBM - 1) + kMoeBM - 1) / kMoeBM * kMoeBM;
+}
+
+extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
+                            int D, int E, int top, int32_t* ids, float* weights, void* stream) {
+    B2_REQUIRE(T >= 0 && D > 0 && E > 0 && top >= 1 && top <= E, B2_EINVAL, "moe_route: bad sizes D=%d E=%d top=%d", D, E, top);
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(h && w_router && ids && weights, B2_EINVAL, "moe_route: null pointer");
+    const int warps = 4;
+    const size_t smem = (size_t)warps * E * sizeof(float);
+    B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "moe_route: %d experts do not fit shared memory", E);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, (moe_route_kernel<A><<<(T + warps - 1) / warps, warps * 32, smem, st>>>(
+        static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, T, D, E, top, ids, weights)));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_moe_align(const int32_t* ids, int n, int E, int cap, int32_t* sorted, int32_t* tile_expert, int32_t* place,
+                            void* stream) {
+    B2_REQUIRE(n >= 0 && E > 0 && cap % kMoeBM == 0 && cap >= b2_moe_capacity(n, E), B2_EINVAL,
+               "moe_align: capacity %d below %d for %d rows over %d experts", cap, b2_moe_capacity(n, E), n, E);
+    if (n == 0) return B2_OK;
+    B2_REQUIRE(ids && sorted && tile_expert && place, B2_EINVAL, "moe_align: null pointer");
+    const size_t smem = (size_t)3 * E * sizeof(int);
+    B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "moe_align: %d experts do not fit shared memory", E);
+    moe_align_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(ids, n, E, cap, sorted, tile_expert, place);
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gate, const void* w_up, const void* w_down,
+                              int act_dtype, int T, int D, int F, int top, int cap, const int32_t* sorted,
+                              const int32_t* tile_expert, const int32_t* place, const float* weights, void* act, float* rows,
+                              void* y, int64_t y_stride, void* stream) {
+    B2_REQUIRE(T >= 0 && D > 0 && F > 0 && top >= 1 && cap % kMoeBM == 0, B2_EINVAL, "moe_experts: bad sizes");
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(h && w_gate && w_up && w_down && sorted && tile_expert && place && weights && act && rows && y, B2_EINVAL,
+               "moe_experts: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int tiles = cap / kMoeBM;
+    const int ve = act_dtype == B2_ACT_BF16 ? 8 : 4;
+    const bool vec1 = D % ve == 0 && h_stride % ve == 0 && b2_aligned16(h) && b2_aligned16(w_gate) && b2_aligned16(w_up);
+    const bool vec2 = F % ve == 0 && b2_aligned16(act) && b2_aligned16(w_down);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        moe_gate_up_kernel<A><<<dim3(tiles, (F + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
+            static_cast<const A*>(h), h_stride, static_cast<const A*>(w_gate), static_cast<const A*>(w_up), sorted, tile_expert,
+            top, D, F, vec1, static_cast<A*>(act));
+        moe_down_kernel<A><<<dim3(tiles, (D + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
+            static_cast<const A*>(act), static_cast<const A*>(w_down), sorted, tile_expert, D, F, vec2, rows);
+        moe_combine_kernel<A><<<T, 256, 0, st>>>(rows, place, weights, top, D, static_cast<A*>(y), y_stride);
+    });
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}

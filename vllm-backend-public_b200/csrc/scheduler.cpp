@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <deque>
+#include <functional>
 #include <unordered_map>
 #include <vector>
 
@@ -30,6 +31,7 @@ struct Req {
     int64_t admit_seq = 0; // admission order, for the preemption victim choice
     bool running = false;  // holds blocks
     bool resumed = false;  // being recomputed after a preemption: its next token is already known
+    int state_slot = -1;   // per-sequence state slot, held while the request holds blocks
 };
 
 }  // namespace
@@ -47,12 +49,20 @@ struct b2_scheduler {
     std::vector<int64_t> decode_ids, slot_mapping, prefill_ids, prefill_slots, preempted, finished;
     std::vector<int32_t> block_tables, seq_lens, prefill_start, prefill_len, prefill_bt;
     std::vector<uint8_t> prefill_last;
+    std::vector<int32_t> free_slots;   // stack of state slots: back() is handed out next (lowest first)
+    std::vector<int32_t> decode_slots, prefill_slots_state;
 };
 
 static void sched_release(b2_scheduler* s, Req& r) {
     if (r.running) {
         b2_bm_free_seq(s->bm, r.id);
         r.running = false;
+        if (r.state_slot >= 0) {
+            // keep the stack sorted so that the lowest free slot is always handed out next
+            s->free_slots.insert(std::upper_bound(s->free_slots.begin(), s->free_slots.end(), r.state_slot,
+                                                  std::greater<int32_t>()), r.state_slot);
+            r.state_slot = -1;
+        }
         s->running.erase(std::remove(s->running.begin(), s->running.end(), r.id), s->running.end());
     }
 }
@@ -76,6 +86,7 @@ extern "C" b2_scheduler* b2_sched_create(int64_t num_blocks, int bs, int max_num
     s->max_model_len = max_model_len;
     s->token_budget = max_num_batched_tokens;
     s->max_nb = (max_model_len + bs - 1) / bs;
+    for (int i = max_num_seqs - 1; i >= 0; --i) s->free_slots.push_back(i);
     return s;
 }
 
@@ -163,6 +174,29 @@ static void sched_preempt(b2_scheduler* s, Req& r) {
     s->preempted.push_back(r.id);
 }
 
+static void sched_fill_plan(b2_scheduler* s, b2_step_plan* plan) {
+    plan->n_decode = (int)s->decode_ids.size();
+    plan->max_nb = s->max_nb;
+    plan->decode_ids = s->decode_ids.data();
+    plan->block_tables = s->block_tables.data();
+    plan->seq_lens = s->seq_lens.data();
+    plan->slot_mapping = s->slot_mapping.data();
+    plan->n_prefill = (int)s->prefill_ids.size();
+    plan->n_prefill_tokens = (int)s->prefill_slots.size();
+    plan->prefill_ids = s->prefill_ids.data();
+    plan->prefill_start = s->prefill_start.data();
+    plan->prefill_len = s->prefill_len.data();
+    plan->prefill_last = s->prefill_last.data();
+    plan->prefill_slots = s->prefill_slots.data();
+    plan->prefill_block_tables = s->prefill_bt.data();
+    plan->n_preempted = (int)s->preempted.size();
+    plan->preempted_ids = s->preempted.data();
+    plan->n_finished = (int)s->finished.size();
+    plan->finished_ids = s->finished.data();
+    plan->decode_state_slots = s->decode_slots.data();
+    plan->prefill_state_slots = s->prefill_slots_state.data();
+}
+
 extern "C" int b2_sched_step(b2_scheduler* s, b2_step_plan* plan) {
     if (!s || !plan) {
         b2_set_error("sched_step: bad args");
@@ -172,6 +206,7 @@ extern "C" int b2_sched_step(b2_scheduler* s, b2_step_plan* plan) {
     s->decode_ids.clear(); s->slot_mapping.clear(); s->block_tables.clear(); s->seq_lens.clear();
     s->prefill_ids.clear(); s->prefill_slots.clear(); s->prefill_start.clear(); s->prefill_len.clear();
     s->prefill_last.clear(); s->prefill_bt.clear(); s->preempted.clear(); s->finished.clear();
+    s->decode_slots.clear(); s->prefill_slots_state.clear();
 
     // 0. requests that finished by length when the previous plan ran: free them now
     for (int64_t id : s->finished_pending) {
@@ -214,6 +249,7 @@ extern "C" int b2_sched_step(b2_scheduler* s, b2_step_plan* plan) {
         const int rc = b2_bm_append(s->bm, id, 1, &slot);
         if (rc != B2_OK) return rc;                      // cannot happen: the step was sized above
         s->decode_ids.push_back(id);
+        s->decode_slots.push_back(r.state_slot);
         s->slot_mapping.push_back(slot);
         r.generated += 1;                                // the token this step samples
         r.resumed = false;
@@ -241,8 +277,10 @@ extern "C" int b2_sched_step(b2_scheduler* s, b2_step_plan* plan) {
         if (chunk > room) chunk = (int)room;
         if (chunk <= 0) return false;
         if (!r.running) {
-            if (b2_bm_alloc_seq(s->bm, r.id, 0) != B2_OK) return false;
+            if (s->free_slots.empty() || b2_bm_alloc_seq(s->bm, r.id, 0) != B2_OK) return false;
             r.running = true;
+            r.state_slot = s->free_slots.back();
+            s->free_slots.pop_back();
             r.admit_seq = s->admit_counter++;
             s->running.push_back(r.id);
         }
@@ -250,6 +288,7 @@ extern "C" int b2_sched_step(b2_scheduler* s, b2_step_plan* plan) {
         s->prefill_slots.resize(off + chunk);
         if (b2_bm_append(s->bm, r.id, chunk, s->prefill_slots.data() + off) != B2_OK) return false;
         s->prefill_ids.push_back(r.id);
+        s->prefill_slots_state.push_back(r.state_slot);
         s->prefill_start.push_back(r.computed);
         s->prefill_len.push_back(chunk);
         r.computed += chunk;
@@ -299,23 +338,110 @@ extern "C" int b2_sched_step(b2_scheduler* s, b2_step_plan* plan) {
         if (rc != B2_OK) return rc;
     }
 
-    plan->n_decode = n_decode;
-    plan->max_nb = max_nb;
-    plan->decode_ids = s->decode_ids.data();
-    plan->block_tables = s->block_tables.data();
-    plan->seq_lens = s->seq_lens.data();
-    plan->slot_mapping = s->slot_mapping.data();
-    plan->n_prefill = n_prefill;
-    plan->n_prefill_tokens = (int)s->prefill_slots.size();
-    plan->prefill_ids = s->prefill_ids.data();
-    plan->prefill_start = s->prefill_start.data();
-    plan->prefill_len = s->prefill_len.data();
-    plan->prefill_last = s->prefill_last.data();
-    plan->prefill_slots = s->prefill_slots.data();
-    plan->prefill_block_tables = s->prefill_bt.data();
-    plan->n_preempted = (int)s->preempted.size();
-    plan->preempted_ids = s->preempted.data();
-    plan->n_finished = (int)s->finished.size();
-    plan->finished_ids = s->finished.data();
+    sched_fill_plan(s, plan);
+    return B2_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// replay mode: the caller dictates the step
+// ---------------------------------------------------------------------------------------------
+extern "C" int b2_sched_step_explicit(b2_scheduler* s, const int64_t* ids, const int32_t* counts, int n, b2_step_plan* plan) {
+    if (!s || !plan || n < 0 || (n > 0 && (!ids || !counts))) {
+        b2_set_error("sched_step_explicit: bad args");
+        return B2_EINVAL;
+    }
+    const int bs = s->bs, max_nb = s->max_nb;
+    // validate the whole step first: nothing is applied unless all of it fits
+    int64_t need_blocks = 0;
+    int new_seqs = 0;
+    for (int i = 0; i < n; ++i) {
+        if (counts[i] <= 0) {
+            b2_set_error("sched_step_explicit: entry %d has %d tokens", i, counts[i]);
+            return B2_EINVAL;
+        }
+        for (int j = 0; j < i; ++j)
+            if (ids[j] == ids[i]) {
+                b2_set_error("sched_step_explicit: request %lld appears twice in one step", (long long)ids[i]);
+                return B2_EINVAL;
+            }
+        auto it = s->reqs.find(ids[i]);
+        const int64_t len = it == s->reqs.end() ? 0 : b2_bm_seq_len(s->bm, ids[i]);
+        if (it == s->reqs.end()) ++new_seqs;
+        if (len + counts[i] > (int64_t)max_nb * bs) {
+            b2_set_error("sched_step_explicit: request %lld would hold %lld tokens, above max_model_len %d", (long long)ids[i],
+                         (long long)(len + counts[i]), s->max_model_len);
+            return B2_EINVAL;
+        }
+        need_blocks += blocks_for(len + counts[i], bs) - blocks_for(len, bs);
+    }
+    if (need_blocks > b2_bm_num_free(s->bm)) {
+        b2_set_error("sched_step_explicit: the step needs %lld blocks, %lld are free", (long long)need_blocks,
+                     (long long)b2_bm_num_free(s->bm));
+        return B2_ENOMEM;
+    }
+    if ((int)s->running.size() + new_seqs > s->max_num_seqs || new_seqs > (int)s->free_slots.size()) {
+        b2_set_error("sched_step_explicit: %d new sequences on top of %d live ones, max_num_seqs %d", new_seqs,
+                     (int)s->running.size(), s->max_num_seqs);
+        return B2_ENOMEM;
+    }
+    s->decode_ids.clear(); s->slot_mapping.clear(); s->block_tables.clear(); s->seq_lens.clear();
+    s->prefill_ids.clear(); s->prefill_slots.clear(); s->prefill_start.clear(); s->prefill_len.clear();
+    s->prefill_last.clear(); s->prefill_bt.clear(); s->preempted.clear(); s->finished.clear();
+    s->decode_slots.clear(); s->prefill_slots_state.clear();
+    for (int i = 0; i < n; ++i) {
+        auto it = s->reqs.find(ids[i]);
+        if (it == s->reqs.end()) {
+            Req r;
+            r.id = ids[i];
+            r.prompt_len = r.orig_prompt = 0;
+            r.max_new = 1;
+            it = s->reqs.emplace(ids[i], r).first;
+            const int rc = b2_bm_alloc_seq(s->bm, ids[i], 0);
+            if (rc != B2_OK) return rc;
+            Req& q = it->second;
+            q.running = true;
+            q.admit_seq = s->admit_counter++;
+            q.state_slot = s->free_slots.back();
+            s->free_slots.pop_back();
+            s->running.push_back(q.id);
+        }
+        Req& r = it->second;
+        const int64_t len = b2_bm_seq_len(s->bm, r.id);
+        if (counts[i] == 1 && len > 0) {
+            int64_t slot = 0;
+            const int rc = b2_bm_append(s->bm, r.id, 1, &slot);
+            if (rc != B2_OK) return rc;
+            s->decode_ids.push_back(r.id);
+            s->decode_slots.push_back(r.state_slot);
+            s->slot_mapping.push_back(slot);
+        } else {
+            const size_t off = s->prefill_slots.size();
+            s->prefill_slots.resize(off + counts[i]);
+            const int rc = b2_bm_append(s->bm, r.id, counts[i], s->prefill_slots.data() + off);
+            if (rc != B2_OK) return rc;
+            s->prefill_ids.push_back(r.id);
+            s->prefill_slots_state.push_back(r.state_slot);
+            s->prefill_start.push_back((int32_t)len);
+            s->prefill_len.push_back(counts[i]);
+            s->prefill_last.push_back(0);
+        }
+        r.computed += counts[i];
+        r.prompt_len = r.orig_prompt = r.computed;
+    }
+    const int n_decode = (int)s->decode_ids.size(), n_prefill = (int)s->prefill_ids.size();
+    if (n_decode) {
+        s->block_tables.resize((size_t)n_decode * max_nb);
+        s->seq_lens.resize(n_decode);
+        const int rc = b2_bm_fill_tables(s->bm, s->decode_ids.data(), n_decode, s->block_tables.data(), max_nb,
+                                         s->seq_lens.data());
+        if (rc != B2_OK) return rc;
+    }
+    if (n_prefill) {
+        s->prefill_bt.resize((size_t)n_prefill * max_nb);
+        std::vector<int32_t> lens(n_prefill);
+        const int rc = b2_bm_fill_tables(s->bm, s->prefill_ids.data(), n_prefill, s->prefill_bt.data(), max_nb, lens.data());
+        if (rc != B2_OK) return rc;
+    }
+    sched_fill_plan(s, plan);
     return B2_OK;
 }
