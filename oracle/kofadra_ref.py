@@ -224,8 +224,8 @@ def random_model(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
                 W[f"{p}.mlp.e{e}.gate"] = rnd(ff, D, std=D ** -0.5)
                 W[f"{p}.mlp.e{e}.up"] = rnd(ff, D, std=D ** -0.5)
                 W[f"{p}.mlp.e{e}.down"] = rnd(D, ff, std=ff ** -0.5)
-            W[p + ".mlp.router"] = rnd(E, D, std=2.0 * D ** -0.5)
-            W[p + ".mlp.router.b"] = rnd(E, std=0.5)
+            W[p + ".mlp.router"] = rnd(E, D, std=4.0 * D ** -0.5)
+            W[p + ".mlp.router.b"] = rnd(E, std=1.0)
         if S:
             for q_ in (1, 2) if f else (1,):
                 W[f"{p}.hc{q_}.in"] = rnd(S, std=0.2) + 1.0 / S

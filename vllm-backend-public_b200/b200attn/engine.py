@@ -83,9 +83,9 @@ def _newest_token(r: "Request") -> int:
 
 def _sampleable(logits: torch.Tensor) -> torch.Tensor:
     """b2_sample reads bf16 rows that start on 16-byte boundaries: fp32 logits are rounded, odd vocabularies padded."""
-    if logits.dtype == torch.bfloat16 and (logits.shape[0] <= 1 or logits.stride(0) % 8 == 0):
-        return logits
     V = logits.shape[1]
+    if logits.dtype == torch.bfloat16 and V % 8 == 0 and logits.stride(0) % 8 == 0:
+        return logits
     buf = torch.empty(logits.shape[0], (V + 7) // 8 * 8, dtype=torch.bfloat16, device=logits.device)
     buf[:, :V].copy_(logits)
     return buf[:, :V]

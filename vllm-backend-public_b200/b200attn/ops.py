@@ -615,6 +615,8 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, see
     lib = _lib.load()
     dev = _need_cuda(logits=logits, temperature=temperature, seeds=seeds, out=out, top_k=top_k, top_p=top_p)
     B, V, st = _rows(logits, "logits")
+    if B == 1:
+        st = (V + 7) // 8 * 8            # one row: the stride is never used, only checked
     if temperature is not None and (temperature.dtype != torch.float32 or temperature.shape != (B,)
                                     or not temperature.is_contiguous()):
         raise ValueError("temperature must be a contiguous fp32 [B]")

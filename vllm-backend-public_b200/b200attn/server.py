@@ -89,6 +89,8 @@ class EngineRunner:
             from pathlib import Path
             cfg = resolve_config(self.args.model_name)
             kw = self.args.engine_kwargs()
+            if str(self.args.dtype) in ("float32", "fp32", "float") and getattr(cfg, "family", "llama") != "llama":
+                kw["dtype"] = "float32"          # families with an all-fp32 path honour --dtype float32
             wdir = Path(self.args.model_name) if Path(self.args.model_name).is_dir() else None
             self.tokenizer = load_tokenizer(self.args.model_name, cfg.vocab, self.tokenizer_path)
             group = None
@@ -551,7 +553,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     else:
         args = EngineArgs.from_cli(argv)
     for note, on in (("--device %s ignored: runs on cuda:0" % args.device, args.device not in (None, "cuda", "auto")),
-                     ("--dtype %s served as bfloat16" % args.dtype, args.dtype not in ("auto", "bfloat16")),
+                     ("--dtype %s is served as bfloat16 by the Llama-family models" % args.dtype, args.dtype not in ("auto", "bfloat16")),
                      ("--quantization %s ignored" % args.quantization, bool(args.quantization))):
         if on:
             print("[b200attn] " + note, file=sys.stderr)

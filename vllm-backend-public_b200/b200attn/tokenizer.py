@@ -17,12 +17,12 @@ class ByteTokenizer:
     eos_token_id: Optional[int] = None
 
     def __init__(self, vocab_size: int):
-        if vocab_size < 256:
-            raise ValueError("byte tokenizer needs a vocabulary of at least 256 ids")
-        self.vocab_size = vocab_size
+        if vocab_size < 1:
+            raise ValueError("byte tokenizer needs a vocabulary")
+        self.vocab_size = vocab_size          # below 256 ids the bytes fold into the vocabulary (lossy)
 
     def encode(self, text: str) -> List[int]:
-        return list(text.encode("utf-8"))
+        return [b % self.vocab_size for b in text.encode("utf-8")] if self.vocab_size < 256 else list(text.encode("utf-8"))
 
     def decode(self, ids: List[int]) -> str:
         return bytes(i % 256 for i in ids).decode("utf-8", errors="replace")
