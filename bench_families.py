@@ -1,0 +1,197 @@
+"""`bench.py --family kofadra`: prefill and decode throughput of the Kofadra family at layer sizes of real models
+(random weights), beside the Llama model of equal width, heads, head size and ACTIVE feed-forward width, plus the device
+time of every new kernel with the roofline that bounds it beside the like kernel of the Llama path.
+
+Both models run through the same engine (LLMEngine.replay_step: scheduler, pools, state slots, CUDA-graph decode).
+  prefill   one prompt chunk of T tokens in one step; wall clock around the step (it ends with a stream synchronize)
+  decode    B sequences with `ctx` cached tokens each, one token per sequence per step; CUDA events around the graph replay
+Kernel lines: CUDA events, 3 warm-ups, median of 10, L2 flushed between iterations (a 256 MiB write).
+One JSON line per measurement; fractions are of the measured copy bandwidth / cuBLAS bf16 burst in MEASURED_PEAKS.json.
+"""
+import json
+import statistics
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path[:0] = [str(ROOT / "vllm-backend-public_b200")]
+
+SIZES = {
+    # name: hidden, layers, heads, kv heads, head size, expert width, experts, chosen, vocabulary
+    "2k": dict(hidden=2048, layers=4, heads=16, kv_heads=4, head_dim=128, ff=1024, experts=32, top=4, vocab=32000),
+    "4k": dict(hidden=4096, layers=4, heads=32, kv_heads=8, head_dim=128, ff=1792, experts=64, top=8, vocab=32000),
+}
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    d = json.loads(p.read_text()) if p.exists() else {}
+    return float(d.get("hbm_gbs", 6650.0)), float(d.get("bf16_tflops", 1590.0)), ("measured" if d else "fallback")
+
+
+def _emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def _engine(cfg, B, ctx, T):
+    import torch
+    from b200attn.engine import LLMEngine
+    bs = 16
+    per_seq = (ctx + 64 + bs - 1) // bs
+    blocks = max(B * per_seq, (T + bs - 1) // bs + 1) + 8
+    return LLMEngine(cfg, torch.device("cuda", 0), max_num_seqs=B, max_model_len=max(ctx + 64, T + 16), block_size=bs,
+                     num_blocks=blocks, max_num_batched_tokens=max(T, 8192), seed=0)
+
+
+def _throughput(name, cfg, B, ctx, T, steps):
+    import torch
+    eng = _engine(cfg, B, ctx, T)
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda n: torch.randint(0, cfg.vocab, (n,), generator=g).tolist()          # noqa: E731
+    # prefill: a fresh request of T tokens per step
+    ts = []
+    for i in range(5):
+        toks = rnd(T)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.replay_step([(("p", i), toks, [T - 1])], [("p", i)])
+        ts.append(time.perf_counter() - t0)
+    pre = statistics.median(ts[2:])
+    _emit(bench="prefill", model=name, tokens=T, ms=round(pre * 1e3, 3), tok_per_s=round(T / pre), timing="wall clock around one engine step")
+    # decode: fill B sequences to ctx tokens (prompt chunks of up to 8192 tokens per step), then single tokens
+    per_step = max(1, 8192 // ctx)
+    for lo in range(0, B, per_step):
+        eng.replay_step([(("d", i), rnd(ctx), []) for i in range(lo, min(B, lo + per_step))], [])
+    eng.time_device = True
+    for k in range(steps + 5):
+        if k == 5:
+            eng.stats.device_ms, eng.stats.device_steps = 0.0, 0
+        eng.replay_step([(("d", i), rnd(1), []) for i in range(B)], [])
+    ms = eng.stats.device_ms / max(eng.stats.device_steps, 1)
+    _emit(bench="decode", model=name, batch=B, ctx=ctx, ms_per_step=round(ms, 4), tok_per_s=round(B / ms * 1e3),
+          weight_gib=round(eng.model.weight_bytes() / 2 ** 30, 2), timing="CUDA events around the decode graph replay")
+    eng.close()
+    del eng
+    torch.cuda.empty_cache()
+
+
+def _time(fn, flush, iters=10):
+    import torch
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def _kernels(size, s, B, ctx, T):
+    """Device time of the new kernels and of the like Llama kernels on the same shapes."""
+    import torch
+    from b200attn import ops
+    dev = torch.device("cuda", 0)
+    HBM, TF, src = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    D, H, G, d, F, E, top = s["hidden"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"], s["top"]
+    bf = torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)          # noqa: E731
+
+    def line(kernel, phase, ms, bytes_=0, flops=0, like=None):
+        gbs, tfs = bytes_ / ms / 1e6, flops / ms / 1e9
+        _emit(bench="kernel", size=size, kernel=kernel, phase=phase, ms=round(ms, 4), gb_per_s=round(gbs, 1),
+              tflop_per_s=round(tfs, 2), frac_hbm=round(gbs / HBM, 3), frac_bf16=round(tfs / TF, 4), peaks=src, like=like)
+
+    S, chunk = 2, 1024
+    for phase, n_seq, q_len, c in (("prefill", 1, T, 0), ("decode", B, 1, ctx)):
+        rows = n_seq * q_len
+        nb_seq = (c + q_len + 15) // 16
+        tables = torch.arange(n_seq * nb_seq, dtype=torch.int32, device=dev).view(n_seq, nb_seq)
+        batch = ops.SeqBatch(i32([i * q_len for i in range(n_seq + 1)]), i32([c] * n_seq), tables, i32(list(range(n_seq))),
+                             n_seq, rows)
+        # ---- residual streams + norm  |  like: fused residual add + RMS norm
+        x = torch.randn(rows, S, D, device=dev)
+        y = torch.randn(rows, D, device=dev).to(bf)
+        mix, ow, iw, nw = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.ones(S, device=dev), torch.ones(D, device=dev)
+        ms = _time(lambda: ops.hc_step(x, y, mix, ow, iw, nw, 1e-6, h_dtype=bf), flush)
+        line("hc_step (2 fp32 streams)", phase, ms, bytes_=rows * D * (2 * S * 4 + 2 + 2), like="rms_norm")
+        res, wn = torch.randn(rows, D, device=dev).to(bf), torch.ones(D, device=dev).to(bf)
+        ms = _time(lambda: ops.rms_norm(y, wn, 1e-6, residual=res), flush)
+        line("rms_norm (Llama, bf16 residual)", phase, ms, bytes_=rows * D * 2 * 4)
+        # ---- attention  |  like: tcgen05 prompt attention / paged decode
+        kc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        vc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        q = torch.randn(rows, H, d, device=dev).to(bf)
+        ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, chunk, sink=1.0), flush)
+        if phase == "prefill":
+            pairs = sum(min(p % chunk, p) + 1 for p in range(T))               # visible (query, key) pairs per head
+            line("chunk_attention", phase, ms, flops=4 * pairs * H * d, like="prefill_attention")
+            cu, cs = i32([0, T]), i32([0])
+            ms = _time(lambda: ops.prefill_attention(q, kc, vc, tables, cu, cs, total_tokens=T), flush)
+            line("prefill_attention (Llama, tcgen05, causal)", phase, ms, flops=4 * (T * (T + 1) // 2) * H * d)
+        else:
+            seen = min((c % chunk) + 1, c + 1)
+            line("chunk_attention", phase, ms, bytes_=n_seq * seen * G * 2 * d * 2, like="paged_decode")
+            sl = i32([c + 1] * n_seq)
+            ms = _time(lambda: ops.paged_decode(q, kc, vc, tables, sl), flush)
+            line("paged_decode (Llama)", phase, ms, bytes_=n_seq * (c + 1) * G * 2 * d * 2)
+        # ---- delta rule: scan (+ prep + out); no like kernel in the Llama path
+        C = 2 * G * d + H * d
+        proj = torch.randn(rows, C + H * d + 2 * H, device=dev).to(bf)
+        conv_w, A, dtb = torch.randn(C, 4, device=dev) * 0.5, -torch.ones(H, device=dev), torch.zeros(H, device=dev)
+        cstate = torch.zeros(n_seq, 3, C, dtype=bf, device=dev)
+        state = torch.zeros(n_seq, H, d, d, device=dev)
+        ms = _time(lambda: ops.delta_prep(proj, C + H * d, C + H * d + H, H, G, d, d, 4, conv_w, A, dtb, batch, cstate), flush)
+        line("delta_prep (+ conv state)", phase, ms, bytes_=rows * (C * 2 + C * 4 + 8 * H))
+        qkv, beta, decay = ops.delta_prep(proj, C + H * d, C + H * d + H, H, G, d, d, 4, conv_w, A, dtb, batch, cstate)
+        ms = _time(lambda: ops.delta_scan(qkv, beta, decay, H, G, d, d, batch, state), flush)
+        line("delta_scan", phase, ms, bytes_=n_seq * H * d * d * 4 * 2 + rows * (C + H * d) * 4, flops=6 * rows * H * d * d)
+        o = ops.delta_scan(qkv, beta, decay, H, G, d, d, batch, state)
+        ms = _time(lambda: ops.delta_out(o, proj, C, nw[:d].contiguous(), 1e-6), flush)
+        line("delta_out", phase, ms, bytes_=rows * H * d * (4 + 2 + 2))
+        # ---- experts  |  like: the dense gated feed-forward of equal active width (two cuBLAS GEMMs + silu_and_mul)
+        h = torch.randn(rows, D, device=dev).to(bf)
+        wr, rb = (torch.randn(E, D, device=dev) * D ** -0.5).to(bf), torch.zeros(E, device=dev)
+        wg, wu = (torch.randn(E, F, D, device=dev) * D ** -0.5).to(bf), (torch.randn(E, F, D, device=dev) * D ** -0.5).to(bf)
+        wd = (torch.randn(E, D, F, device=dev) * F ** -0.5).to(bf)
+        ms = _time(lambda: ops.moe_route(h, wr, rb, top), flush)
+        line("moe_route", phase, ms, bytes_=rows * D * 2 + E * D * 2, flops=2 * rows * E * D)
+        ids, wts = ops.moe_route(h, wr, rb, top)
+        ms = _time(lambda: ops.moe_experts(h, ids, wts, wg, wu, wd), flush)
+        used = min(E, rows * top)
+        line("moe_experts (align + 2 grouped products + combine)", phase, ms, bytes_=used * 3 * F * D * 2,
+             flops=6 * rows * top * F * D, like="dense gated MLP")
+        w1, w2 = (torch.randn(2 * top * F, D, device=dev) * D ** -0.5).to(bf), (torch.randn(D, top * F, device=dev) * 0.02).to(bf)
+        ms = _time(lambda: torch.nn.functional.linear(ops.silu_and_mul(torch.nn.functional.linear(h, w1)), w2), flush)
+        line("dense gated MLP (Llama: cuBLAS + silu_and_mul)", phase, ms, bytes_=3 * top * F * D * 2, flops=6 * rows * top * F * D)
+        del wg, wu, wd, w1, w2, kc, vc, state
+        torch.cuda.empty_cache()
+
+
+def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
+    import torch
+    from b200attn.kofadra import bench_config
+    from b200attn.model import ModelConfig
+    if family != "kofadra":
+        raise SystemExit(f"unknown family {family!r}")
+    B, ctx, T = 64, 2048, 4096
+    for name in sizes:
+        s = SIZES[name]
+        kcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"], s["top"],
+                            s["vocab"], name=f"kofadra-{name}")
+        lcfg = ModelConfig(f"llama-{name}", s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["top"] * s["ff"], s["vocab"],
+                           max_position=8192)
+        _emit(bench="config", size=name, **s, kofadra_params=kcfg.params, llama_params=lcfg.params, prefill_tokens=T,
+              decode_batch=B, decode_ctx=ctx, data="synthetic", dtype="bf16")
+        _throughput(kcfg.name, kcfg, B, ctx, T, steps)
+        _throughput(lcfg.name, lcfg, B, ctx, T, steps)
+        if kernels:
+            _kernels(name, s, B, ctx, T)
+        torch.cuda.empty_cache()

@@ -68,7 +68,7 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
                                        const int32_t* __restrict__ block_tables, int max_nb,
                                        const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start, int n_seq,
                                        int rows, int H, int G, int dk, int dv, int bs, float scale, int chunk, float sink,
-                                       float sink_logit, T* __restrict__ out) {
+                                       float sink_logit, int skip_rows_from, T* __restrict__ out) {
     extern __shared__ float q_sm[];                  // [warps, dk]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int item = blockIdx.x * (blockDim.x >> 5) + wid;       // (row, head)
@@ -77,6 +77,7 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
     const int seq = b2::seq_of_row(cu_q, n_seq, row);
     const int ctx = ctx_start[seq];
     T* dst = out + (size_t)item * dv;
+    if (skip_rows_from > 0 && ctx >= 0 && cu_q[seq + 1] - cu_q[seq] >= skip_rows_from) return;    // the tile kernel's
     if (ctx < 0) {
         for (int i = lane; i < dv; i += 32) b2::st(dst + i, 0.f);
         return;
@@ -132,6 +133,189 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
     }
 }
 
+// ------------------------------------------------------------------------------------------------- tiled prompt kernel
+// bf16, dk and dv multiples of 16: one CTA = 64 consecutive query rows of one sequence x one head, four warps of 16 rows.
+// Keys are walked 64 at a time from the first row's block start to the last row's position (at most chunk + 63 keys
+// with a mask, the whole prefix without): K and V tiles are gathered from the pages into shared memory, S = Q K^T and
+// O += P V run on mma.sync m16n8k16 with ldmatrix operands, the online softmax lives in the accumulator registers
+// (exp2 with the scale folded in, the sink seeding the running maximum and denominator).  Sequences with fewer than
+// kTileMinRows rows (decode rows) are left to the warp kernel above.
+constexpr int kTQ = 64, kTK = 64, kTileMinRows = 16;
+
+template <int DKT, int DVT>
+__global__ void __launch_bounds__(128)
+chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                            const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_tables, int max_nb,
+                            const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start, int n_seq, int H, int G,
+                            int bs, float scale_log2, int chunk, float sink, float sink_logit_log2,
+                            __nv_bfloat16* __restrict__ out) {
+    constexpr int DK = 16 * DKT, DV = 16 * DVT, LDK = DK + 8, LDV = DV + 8;
+    extern __shared__ __align__(16) unsigned char tile_smem[];
+    __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(tile_smem);      // [64][LDK]
+    __nv_bfloat16* k_sm = q_sm + kTQ * LDK;                                 // [64][LDK]
+    __nv_bfloat16* v_sm = k_sm + kTK * LDK;                                 // [64][LDV]
+    __shared__ int s_info[2];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    if (tid == 0) {
+        int want = blockIdx.x, found = -1, t0 = 0;
+        for (int s = 0; s < n_seq; ++s) {
+            const int len = cu_q[s + 1] - cu_q[s];
+            if (len < kTileMinRows || ctx_start[s] < 0) continue;
+            const int nt = (len + kTQ - 1) / kTQ;
+            if (want < nt) { found = s; t0 = want * kTQ; break; }
+            want -= nt;
+        }
+        s_info[0] = found;
+        s_info[1] = t0;
+    }
+    __syncthreads();
+    const int seq = s_info[0], t0 = s_info[1];
+    if (seq < 0) return;
+    const int hh = blockIdx.y, g = hh / (H / G);
+    const int r0 = cu_q[seq] + t0;
+    const int rows = min(kTQ, cu_q[seq + 1] - r0);
+    const int p0 = ctx_start[seq] + t0, p_last = p0 + rows - 1;
+    const int klo = chunk > 0 ? (p0 / chunk) * chunk : 0;
+    const int32_t* bt = block_tables + (size_t)seq * max_nb;
+
+    for (int idx = tid; idx < kTQ * (DK / 8); idx += 128) {
+        const int r = idx / (DK / 8), c = (idx % (DK / 8)) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(r0 + r) * H + hh) * DK + c);
+        *reinterpret_cast<uint4*>(q_sm + r * LDK + c) = v;
+    }
+    const int gq = lane >> 2, tq = lane & 3;
+    const int i0 = p0 + w * 16 + gq, i1 = i0 + 8;                           // positions of this thread's two rows
+    const int lo0 = chunk > 0 ? (i0 / chunk) * chunk : 0, lo1 = chunk > 0 ? (i1 / chunk) * chunk : 0;
+    const int w_first = p0 + w * 16, w_last = w_first + 15;
+    const int w_lo = chunk > 0 ? (w_first / chunk) * chunk : 0;
+    float m0 = sink > 0.f ? sink_logit_log2 : -INFINITY, m1 = m0;
+    float l0 = tq == 0 ? sink : 0.f, l1 = l0;                               // partial sums per lane; the sink counted once
+    float o[2 * DVT][4];
+#pragma unroll
+    for (int n = 0; n < 2 * DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const uint32_t q_base = b2::smem_u32(q_sm), k_base = b2::smem_u32(k_sm), v_base = b2::smem_u32(v_sm);
+
+    for (int kv0 = klo; kv0 <= p_last; kv0 += kTK) {
+        __syncthreads();                                                    // the previous tile is consumed (and Q is stored)
+        for (int idx = tid; idx < kTK * (DK / 8); idx += 128) {
+            const int key = idx / (DK / 8), c = (idx % (DK / 8)) * 8, j = kv0 + key;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (j <= p_last) v = *reinterpret_cast<const uint4*>(k_cache + (((size_t)bt[j / bs] * G + g) * bs + j % bs) * DK + c);
+            *reinterpret_cast<uint4*>(k_sm + key * LDK + c) = v;
+        }
+        for (int idx = tid; idx < kTK * (DV / 8); idx += 128) {
+            const int key = idx / (DV / 8), c = (idx % (DV / 8)) * 8, j = kv0 + key;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (j <= p_last) v = *reinterpret_cast<const uint4*>(v_cache + (((size_t)bt[j / bs] * G + g) * bs + j % bs) * DV + c);
+            *reinterpret_cast<uint4*>(v_sm + key * LDV + c) = v;
+        }
+        __syncthreads();
+        if (kv0 > w_last || kv0 + kTK - 1 < w_lo) continue;                 // nothing in this tile is visible to the warp's rows
+        float sc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < DKT; ++kk) {
+            uint32_t a0, a1, a2, a3;
+            b2::ldmatrix_x4(q_base + 2u * ((w * 16 + (lane & 15)) * LDK + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                uint32_t b0, b1, b2_, b3;
+                const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), dim = kk * 16 + ((lane >> 3) & 1) * 8;
+                b2::ldmatrix_x4(k_base + 2u * (key * LDK + dim), b0, b1, b2_, b3);
+                b2::mma_bf16_16816(sc[2 * n2], a0, a1, a2, a3, b0, b1);
+                b2::mma_bf16_16816(sc[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kv0 + n * 8 + 2 * tq + (e & 1);
+                const bool ok = e < 2 ? (j >= lo0 && j <= i0) : (j >= lo1 && j <= i1);
+                sc[n][e] = ok ? sc[n][e] * scale_log2 : -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = exp2f(m0 - mu0), c1 = exp2f(m1 - mu1);             // exp2(-inf) = 0: nothing accumulated yet
+        m0 = mn0;
+        m1 = mn1;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            sc[n][0] = exp2f(sc[n][0] - mu0);
+            sc[n][1] = exp2f(sc[n][1] - mu0);
+            sc[n][2] = exp2f(sc[n][2] - mu1);
+            sc[n][3] = exp2f(sc[n][3] - mu1);
+            s0 += sc[n][0] + sc[n][1];
+            s1 += sc[n][2] + sc[n][3];
+        }
+        l0 = l0 * c0 + s0;
+        l1 = l1 * c1 + s1;
+#pragma unroll
+        for (int n = 0; n < 2 * DVT; ++n) {
+            o[n][0] *= c0;
+            o[n][1] *= c0;
+            o[n][2] *= c1;
+            o[n][3] *= c1;
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t a0 = b2::pack_bf16x2(sc[2 * ks][0], sc[2 * ks][1]), a1 = b2::pack_bf16x2(sc[2 * ks][2], sc[2 * ks][3]);
+            const uint32_t a2 = b2::pack_bf16x2(sc[2 * ks + 1][0], sc[2 * ks + 1][1]),
+                           a3 = b2::pack_bf16x2(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < DVT; ++n2) {
+                uint32_t b0, b1, b2_, b3;
+                const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = n2 * 16 + (lane >> 4) * 8;
+                b2::ldmatrix_x4_trans(v_base + 2u * (key * LDV + col), b0, b1, b2_, b3);
+                b2::mma_bf16_16816(o[2 * n2], a0, a1, a2, a3, b0, b1);
+                b2::mma_bf16_16816(o[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    const int ra = w * 16 + gq, rb = ra + 8;
+#pragma unroll
+    for (int n = 0; n < 2 * DVT; ++n) {
+        const int col = n * 8 + 2 * tq;
+        if (ra < rows)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(r0 + ra) * H + hh) * DV + col) = b2::pack_bf16x2(o[n][0] * inv0, o[n][1] * inv0);
+        if (rb < rows)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(r0 + rb) * H + hh) * DV + col) = b2::pack_bf16x2(o[n][2] * inv1, o[n][3] * inv1);
+    }
+}
+
+template <int DKT, int DVT>
+int launch_tile(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_tables, int max_nb,
+                const int32_t* cu_q, const int32_t* ctx_start, int n_seq, int T, int H, int G, int bs, float scale, int chunk,
+                float sink, float sink_logit, void* out, cudaStream_t st) {
+    constexpr int DK = 16 * DKT, DV = 16 * DVT;
+    const size_t smem = (size_t)(kTQ * (DK + 8) + kTK * (DK + 8) + kTK * (DV + 8)) * sizeof(__nv_bfloat16);
+    auto kern = chunk_attention_tile_kernel<DKT, DVT>;
+    if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int tiles = (T + kTQ - 1) / kTQ + n_seq;          // upper bound on sum(ceil(len / 64)); spare CTAs leave at once
+    kern<<<dim3(tiles, H), 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
+                                           static_cast<const __nv_bfloat16*>(v_cache), block_tables, max_nb, cu_q, ctx_start,
+                                           n_seq, H, G, bs, scale * 1.4426950408889634f, chunk, sink,
+                                           sink_logit * 1.4426950408889634f, static_cast<__nv_bfloat16*>(out));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
 }  // namespace
 
 extern "C" int b2_qknorm_cache(const void* qkv, int64_t qkv_stride, int act_dtype, int T, int H, int G, int dk, int dv,
@@ -163,9 +347,25 @@ extern "C" int b2_chunk_attention(void* out, const void* q, const void* k_cache,
     const size_t smem = (size_t)warps * dk * sizeof(float);
     B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "chunk_attention: key size %d too large", dk);
     const int items = T * H, blocks = (items + warps - 1) / warps;
+    // prompt chunks of bf16 models with tensor-core friendly head sizes go to the tiled kernel (a sequence needs at least
+    // kTileMinRows rows, so a batch of T rows over n_seq sequences can only hold one when T - n_seq >= kTileMinRows - 1)
+    int skip_from = 0;
+    if (act_dtype == B2_ACT_BF16 && T - n_seq >= kTileMinRows - 1 && dk % 32 == 0 && dv % 32 == 0 && dk <= 128 && dv <= 128 &&
+        b2_aligned16(q) && b2_aligned16(k_cache) && b2_aligned16(v_cache) && b2_aligned16(out)) {
+        skip_from = kTileMinRows;
+        int rc = B2_OK;
+#define B2_TILE(a, b)                                                                                                     \
+    if (dk == 16 * a && dv == 16 * b)                                                                                     \
+        rc = launch_tile<a, b>(q, k_cache, v_cache, block_tables, max_nb, cu_q, ctx_start, n_seq, T, H, G, bs, scale, chunk, \
+                               sink, sink_logit, out, st);
+        B2_TILE(2, 2) B2_TILE(2, 4) B2_TILE(2, 6) B2_TILE(2, 8) B2_TILE(4, 2) B2_TILE(4, 4) B2_TILE(4, 6) B2_TILE(4, 8)
+        B2_TILE(6, 2) B2_TILE(6, 4) B2_TILE(6, 6) B2_TILE(6, 8) B2_TILE(8, 2) B2_TILE(8, 4) B2_TILE(8, 6) B2_TILE(8, 8)
+#undef B2_TILE
+        if (rc != B2_OK) return rc;
+    }
     B2_DISPATCH_ACT(act_dtype, A, (chunk_attention_kernel<A><<<blocks, warps * 32, smem, st>>>(
         static_cast<const A*>(q), static_cast<const A*>(k_cache), static_cast<const A*>(v_cache), block_tables, max_nb, cu_q,
-        ctx_start, n_seq, T, H, G, dk, dv, bs, scale, chunk, sink, sink_logit, static_cast<A*>(out))));
+        ctx_start, n_seq, T, H, G, dk, dv, bs, scale, chunk, sink, sink_logit, skip_from, static_cast<A*>(out))));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }

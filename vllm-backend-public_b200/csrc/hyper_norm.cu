@@ -30,7 +30,7 @@ __global__ void embed_streams_kernel(const T* __restrict__ embed, const int64_t*
 }
 
 template <typename T>
-__global__ void hc_step_kernel(float* __restrict__ x, int S, int D, const T* __restrict__ y, int64_t y_stride,
+__global__ void __launch_bounds__(512) hc_step_kernel(float* __restrict__ x, int S, int D, const T* __restrict__ y, int64_t y_stride,
                                const float* __restrict__ mix, const float* __restrict__ out_w,
                                const float* __restrict__ in_w, const float* __restrict__ norm_w, float eps, int norm_kind,
                                T* __restrict__ h, int64_t h_stride) {
@@ -46,38 +46,64 @@ __global__ void hc_step_kernel(float* __restrict__ x, int S, int D, const T* __r
     __syncthreads();
     float* xt = x + (size_t)t * S * D;
     float sum = 0.f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float xs[kMaxStreams];
+    // four columns per thread and 16-byte accesses to the streams when the width allows it
+    const int W = (D % 4 == 0) ? 4 : 1;
+    for (int d = threadIdx.x * W; d < D; d += blockDim.x * W) {
+        float xs[kMaxStreams][4];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) xs[s] = s < S ? xt[(size_t)s * D + d] : 0.f;
+        for (int s = 0; s < kMaxStreams; ++s) {
+            if (s < S) {
+                if (W == 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(xt + (size_t)s * D + d);
+                    xs[s][0] = v.x; xs[s][1] = v.y; xs[s][2] = v.z; xs[s][3] = v.w;
+                } else {
+                    xs[s][0] = xt[(size_t)s * D + d];
+                    xs[s][1] = xs[s][2] = xs[s][3] = 0.f;
+                }
+            } else {
+                xs[s][0] = xs[s][1] = xs[s][2] = xs[s][3] = 0.f;
+            }
+        }
         if (y) {
-            const float yv = b2::ld(y + (size_t)t * y_stride + d);
-            float nx[kMaxStreams];
+            float yv[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int c = 0; c < W; ++c) yv[c] = b2::ld(y + (size_t)t * y_stride + d + c);
+            float nx[kMaxStreams][4];
 #pragma unroll
             for (int j = 0; j < kMaxStreams; ++j) {
-                float a = 0.f;
-                if (j < S) {
 #pragma unroll
-                    for (int s = 0; s < kMaxStreams; ++s)
-                        if (s < S) a = fmaf(c_mix[s * S + j], xs[s], a);
-                    a = fmaf(c_out[j], yv, a);
-                    xt[(size_t)j * D + d] = a;
+                for (int c = 0; c < 4; ++c) {
+                    float a = 0.f;
+                    if (j < S) {
+#pragma unroll
+                        for (int s = 0; s < kMaxStreams; ++s)
+                            if (s < S) a = fmaf(c_mix[s * S + j], xs[s][c], a);
+                        a = fmaf(c_out[j], yv[c], a);
+                    }
+                    nx[j][c] = a;
                 }
-                nx[j] = a;
+                if (j < S) {
+                    if (W == 4) *reinterpret_cast<float4*>(xt + (size_t)j * D + d) = make_float4(nx[j][0], nx[j][1], nx[j][2], nx[j][3]);
+                    else xt[(size_t)j * D + d] = nx[j][0];
+                }
             }
 #pragma unroll
-            for (int j = 0; j < kMaxStreams; ++j) xs[j] = nx[j];
+            for (int j = 0; j < kMaxStreams; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) xs[j][c] = nx[j][c];
         }
         if (h) {
-            float u = 0.f;
+            for (int c = 0; c < W; ++c) {
+                float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
-                if (s < S) u = fmaf(c_in[s], xs[s], u);
-            u_sm[d] = u;
-            sum += u;
+                for (int s = 0; s < kMaxStreams; ++s)
+                    if (s < S) u = fmaf(c_in[s], xs[s][c], u);
+                u_sm[d + c] = u;
+                sum += u;
+            }
         }
     }
     if (!h) return;
+    __syncthreads();                                 // u_sm is read across threads from here on
     float mean = 0.f;
     if (norm_kind == B2_NORM_LAYER) mean = b2::block_sum(sum, red) / (float)D;
     float sq = 0.f;
@@ -114,7 +140,7 @@ extern "C" int b2_hc_step(float* x, int T, int S, int D, const void* y, int64_t 
     const size_t smem = h ? (size_t)D * sizeof(float) : 0;
     B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "hc_step: width %d does not fit shared memory", D);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int threads = D >= 2048 ? 512 : 256;
+    const int threads = D >= 1024 ? 512 : 256;
     B2_DISPATCH_ACT(act_dtype, A, {
         auto kern = hc_step_kernel<A>;
         if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -21,24 +21,36 @@ namespace {
 constexpr int kMoeBM = 32, kMoeBN = 64, kMoeBK = 32;
 
 // ------------------------------------------------------------------------------------------------- router
+// One CTA per token: the row is staged once as fp32, the warps share the experts (each logit is one warp's dot product
+// with four independent partial sums per lane), then warp 0 picks the `top` largest.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_r,
-                                 const float* __restrict__ bias, int rows, int D, int E, int top,
+                                 const float* __restrict__ bias, int D, int E, int top,
                                  int32_t* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ float z_sm[];                  // [warps, E]
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + wid;
-    if (t >= rows) return;
-    float* z = z_sm + (size_t)wid * E;
+    extern __shared__ float route_sm[];              // h [D] | z [E]
+    float* hs = route_sm;
+    float* z = route_sm + D;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int t = blockIdx.x;
     const T* x = h + (size_t)t * h_stride;
-    for (int e = 0; e < E; ++e) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) hs[i] = b2::ld(x + i);
+    __syncthreads();
+    for (int e = wid; e < E; e += nw) {
         const T* w = w_r + (size_t)e * D;
-        float a = 0.f;
-        for (int i = lane; i < D; i += 32) a = fmaf(b2::ld(x + i), b2::ld(w + i), a);
-        a = b2::warp_sum(a);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int i = lane;
+        for (; i + 96 < D; i += 128) {
+            a0 = fmaf(hs[i], b2::ld(w + i), a0);
+            a1 = fmaf(hs[i + 32], b2::ld(w + i + 32), a1);
+            a2 = fmaf(hs[i + 64], b2::ld(w + i + 64), a2);
+            a3 = fmaf(hs[i + 96], b2::ld(w + i + 96), a3);
+        }
+        for (; i < D; i += 32) a0 = fmaf(hs[i], b2::ld(w + i), a0);
+        const float a = b2::warp_sum((a0 + a1) + (a2 + a3));
         if (lane == 0) z[e] = a + (bias ? bias[e] : 0.f);
     }
-    __syncwarp();
+    __syncthreads();
+    if (wid != 0) return;
     float v0 = 0.f, sum = 0.f;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
@@ -300,12 +312,16 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
     B2_REQUIRE(T >= 0 && D > 0 && E > 0 && top >= 1 && top <= E, B2_EINVAL, "moe_route: bad sizes D=%d E=%d top=%d", D, E, top);
     if (T == 0) return B2_OK;
     B2_REQUIRE(h && w_router && ids && weights, B2_EINVAL, "moe_route: null pointer");
-    const int warps = 4;
-    const size_t smem = (size_t)warps * E * sizeof(float);
-    B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "moe_route: %d experts do not fit shared memory", E);
+    const size_t smem = (size_t)(D + E) * sizeof(float);
+    B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "moe_route: width %d and %d experts do not fit shared memory", D, E);
+    const int warps = E < 8 ? (E < 2 ? 2 : E) : 8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    B2_DISPATCH_ACT(act_dtype, A, (moe_route_kernel<A><<<(T + warps - 1) / warps, warps * 32, smem, st>>>(
-        static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, T, D, E, top, ids, weights)));
+    B2_DISPATCH_ACT(act_dtype, A, {
+        auto kern = moe_route_kernel<A>;
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<T, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, D, E, top, ids,
+                                          weights);
+    });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
