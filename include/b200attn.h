@@ -504,8 +504,13 @@ B2_API int b2_moe_capacity(int n, int E);
 B2_API int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
                         int D, int E, int top, int32_t* ids, float* weights, void* stream);
 B2_API int b2_moe_align(const int32_t* ids, int n, int E, int cap, int32_t* sorted, int32_t* tile_expert, int32_t* place,
-                        void* stream);
+                        int32_t* group_ends /* [E] or NULL */, void* stream);
+B2_API int b2_moe_gather(const void* h, int64_t h_stride, int act_dtype, const int32_t* sorted, int cap, int top, int D,
+                         void* out, void* stream);
+B2_API int b2_moe_combine(const void* rows, int rows_f32, const int32_t* place, const float* weights, int T, int top, int D,
+                          void* y, int64_t y_stride, int act_dtype, void* stream);
 B2_API int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gate, const void* w_up, const void* w_down,
+                          int64_t w13_expert_stride /* elements between experts of w_gate / w_up (>= F*D) */,
                           int act_dtype, int T, int D, int F, int top, int cap, const int32_t* sorted,
                           const int32_t* tile_expert, const int32_t* place, const float* weights, void* act, float* rows,
                           void* y, int64_t y_stride, void* stream);

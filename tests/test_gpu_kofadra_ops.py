@@ -292,6 +292,36 @@ def test_router_and_experts(cuda, T, D, F, E, top, dtype):
             a = R.silu(W64[f"m.e{e}.gate"] @ h[t].to(F64)) * (W64[f"m.e{e}.up"] @ h[t].to(F64))
             want[t] += wt[t, j] * (W64[f"m.e{e}.down"] @ a)
     _close(y, want, 2e-5 if dtype == torch.float32 else 3e-2, "experts")
+    # gate and up as views of the stacked [E, 2F, D] tensor (how the model holds them), and, for a batch large enough,
+    # the grouped-GEMM path: same result
+    gu = torch.cat([stack("gate"), stack("up")], 1).contiguous()
+    y2 = ops.moe_experts(h.to(cuda), idx.to(torch.int32).to(cuda), wt.float().to(cuda), gu[:, :F], gu[:, F:], stack("down"),
+                         w_gate_up=gu)
+    _close(y2, want, 2e-5 if dtype == torch.float32 else 3e-2, "experts (stacked)")
+
+
+def test_experts_large_batch_takes_the_grouped_gemm(cuda, monkeypatch):
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    T, D, F, E, top = 700, 64, 40, 7, 3
+    assert T * top >= ops.MOE_GROUPED_GEMM_MIN_PAIRS
+    h = torch.randn(T, D, generator=g).to(torch.bfloat16).to(cuda)
+    wr = (torch.randn(E, D, generator=g) * 0.5).to(torch.bfloat16).to(cuda)
+    gu = (torch.randn(E, 2 * F, D, generator=g) * D ** -0.5).to(torch.bfloat16).to(cuda)
+    wd = (torch.randn(E, D, F, generator=g) * F ** -0.5).to(torch.bfloat16).to(cuda)
+    ids, wts = ops.moe_route(h, wr, None, top)
+    fast = ops.moe_experts(h, ids, wts, gu[:, :F], gu[:, F:], wd, w_gate_up=gu)
+    monkeypatch.setattr(ops, "MOE_GROUPED_GEMM_MIN_PAIRS", 10 ** 9)
+    own = ops.moe_experts(h, ids, wts, gu[:, :F], gu[:, F:], wd, w_gate_up=gu)
+    _close(fast, own, 2e-2, "grouped GEMM against the tiled kernels")
+    want = torch.zeros(T, D, dtype=F64)
+    hf, guf, wdf = h.double().cpu(), gu.double().cpu(), wd.double().cpu()
+    for t in range(0, T, 37):
+        for j in range(top):
+            e = int(ids[t, j])
+            a = R.silu(guf[e, :F] @ hf[t]) * (guf[e, F:] @ hf[t])
+            want[t] += float(wts[t, j]) * (wdf[e] @ a)
+    _close(fast.cpu()[::37], want[::37], 3e-2, "grouped GEMM against the oracle")
 
 
 def test_experts_do_not_depend_on_the_batch(cuda):

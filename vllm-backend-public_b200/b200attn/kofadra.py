@@ -302,8 +302,10 @@ class KofadraModel:
                 w[p + ".conv"] = torch.cat([w.pop(p + ".mix.q.conv"), w.pop(p + ".mix.k.conv"),
                                             w.pop(p + ".mix.v.conv")]).contiguous()
             if L.mlp:
-                for leaf in ("gate", "up", "down"):
-                    w[f"{p}.mlp.{leaf}"] = torch.stack([w.pop(f"{p}.mlp.e{e}.{leaf}") for e in range(L.mlp.experts)]).contiguous()
+                # gate and up stacked per expert [E, 2F, D] (one grouped product for both); down [E, D, F]
+                w[f"{p}.mlp.gate_up"] = torch.stack([torch.cat([w.pop(f"{p}.mlp.e{e}.gate"), w.pop(f"{p}.mlp.e{e}.up")])
+                                                     for e in range(L.mlp.experts)]).contiguous()
+                w[f"{p}.mlp.down"] = torch.stack([w.pop(f"{p}.mlp.e{e}.down") for e in range(L.mlp.experts)]).contiguous()
         self._ones = torch.ones(self.S, dtype=torch.float32, device=self.dev)
 
     def weight_bytes(self) -> int:
@@ -392,7 +394,8 @@ class KofadraModel:
     def _mlp(self, li: int, h: torch.Tensor) -> torch.Tensor:
         f, w, p = self.cfg.layer_specs[li].mlp, self.w, f"l{li}.mlp"
         ids, wts = ops.moe_route(h, w[p + ".router"], w[p + ".router.b"], f.top)
-        return ops.moe_experts(h, ids, wts, w[p + ".gate"], w[p + ".up"], w[p + ".down"])
+        gu = w[p + ".gate_up"]
+        return ops.moe_experts(h, ids, wts, gu[:, :f.ff], gu[:, f.ff:], w[p + ".down"], w_gate_up=gu)
 
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, n_decode: int,
                 dec_block_tables: Optional[torch.Tensor], dec_seq_lens: Optional[torch.Tensor], prefill,

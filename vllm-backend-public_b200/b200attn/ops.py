@@ -844,31 +844,55 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
     return ids, wts
 
 
+# Above this many (token, choice) pairs the two expert products of a bf16 batch are compute bound and go to the vendor's
+# grouped GEMM (torch._grouped_mm over the expert-sorted rows, group offsets read on the device); below it they stream the
+# expert weights once and run on this library's tiled kernels, as does everything in fp32.
+MOE_GROUPED_GEMM_MIN_PAIRS = 2048
+
+
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                w_down: torch.Tensor) -> torch.Tensor:
+                w_down: torch.Tensor, w_gate_up: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[t] = sum_j wts[t, j] * W_down[e] (silu(W_gate[e] h[t]) * (W_up[e] h[t])), e = ids[t, j].
-    w_gate, w_up [E, F, D]; w_down [E, D, F].  Sorting by expert, both grouped products and the weighted sum run on the
-    device without a host read (b2_moe_align, b2_moe_experts)."""
+    w_gate, w_up [E, F, D]; w_down [E, D, F]; w_gate_up [E, 2F, D] (optional): the two stacked per expert -- w_gate and
+    w_up may be views of it.  Sorting by expert (b2_moe_align), both products and the weighted sum (in fp32, choice order)
+    run on the device without a host read: b2_moe_experts, or for large bf16 batches b2_moe_gather -> grouped GEMM ->
+    b2_silu_and_mul -> grouped GEMM -> b2_moe_combine."""
     lib = _lib.load()
     dev = _need_cuda(h=h, ids=ids, wts=wts, w_gate=w_gate, w_up=w_up, w_down=w_down)
     T, D, hs = _mat(h, "h")
     E, F, _ = w_gate.shape
     top = ids.shape[1]
     for name, w, shape in (("w_gate", w_gate, (E, F, D)), ("w_up", w_up, (E, F, D)), ("w_down", w_down, (E, D, F))):
-        if w.dtype != h.dtype or tuple(w.shape) != shape or not w.is_contiguous():
-            raise ValueError(f"{name} must be contiguous {shape} of h's dtype")
+        if w.dtype != h.dtype or tuple(w.shape) != shape or w.stride(2) != 1 or w.stride(1) != shape[2]:
+            raise ValueError(f"{name} must be {shape} of h's dtype with contiguous rows")
+    if w_gate.stride(0) != w_up.stride(0) or not w_down.is_contiguous():
+        raise ValueError("w_gate / w_up must share their expert stride, w_down must be contiguous")
     if ids.dtype != torch.int32 or not ids.is_contiguous() or tuple(ids.shape) != (T, top):
         raise ValueError("ids must be contiguous int32 [T, top]")
     _f32(wts, "wts", (T, top))
     n = T * top
     cap = lib.b2_moe_capacity(n, E)
-    meta = torch.empty(cap + cap // lib.b2_moe_tile_rows() + n, dtype=torch.int32, device=dev)
-    srt, tile_e, place = meta[:cap], meta[cap:cap + cap // lib.b2_moe_tile_rows()], meta[cap + cap // lib.b2_moe_tile_rows():]
-    _lib.check(lib.b2_moe_align(_ptr(ids), n, E, cap, _ptr(srt), _ptr(tile_e), _ptr(place), _stream(dev)))
+    tiles = cap // lib.b2_moe_tile_rows()
+    grouped = (w_gate_up is not None and h.dtype == torch.bfloat16 and n >= MOE_GROUPED_GEMM_MIN_PAIRS and D % 8 == 0
+               and F % 8 == 0 and hasattr(torch, "_grouped_mm"))
+    meta = torch.empty(cap + tiles + n + E, dtype=torch.int32, device=dev)
+    srt, tile_e, place, ends = meta[:cap], meta[cap:cap + tiles], meta[cap + tiles:cap + tiles + n], meta[cap + tiles + n:]
+    _lib.check(lib.b2_moe_align(_ptr(ids), n, E, cap, _ptr(srt), _ptr(tile_e), _ptr(place), _ptr(ends) if grouped else None,
+                                _stream(dev)))
+    y = torch.empty(T, D, dtype=h.dtype, device=dev)
+    if grouped:
+        if tuple(w_gate_up.shape) != (E, 2 * F, D) or not w_gate_up.is_contiguous() or w_gate_up.dtype != h.dtype:
+            raise ValueError("w_gate_up must be contiguous [E, 2F, D] of h's dtype")
+        a = torch.empty(cap, D, dtype=h.dtype, device=dev)
+        _lib.check(lib.b2_moe_gather(_ptr(h), hs, _act(h, "h"), _ptr(srt), cap, top, D, _ptr(a), _stream(dev)))
+        gu = torch._grouped_mm(a, w_gate_up.transpose(1, 2), offs=ends)              # [cap, 2F]; rows past the last group unset
+        act = silu_and_mul(gu)
+        rows = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)             # [cap, D]
+        _lib.check(lib.b2_moe_combine(_ptr(rows), 0, _ptr(place), _ptr(wts), T, top, D, _ptr(y), D, _act(h, "h"), _stream(dev)))
+        return y
     act = torch.empty(cap, F, dtype=h.dtype, device=dev)
     rows = torch.empty(cap, D, dtype=torch.float32, device=dev)
-    y = torch.empty(T, D, dtype=h.dtype, device=dev)
-    _lib.check(lib.b2_moe_experts(_ptr(h), hs, _ptr(w_gate), _ptr(w_up), _ptr(w_down), _act(h, "h"), T, D, F, top, cap,
-                                  _ptr(srt), _ptr(tile_e), _ptr(place), _ptr(wts), _ptr(act), _ptr(rows), _ptr(y), D,
+    _lib.check(lib.b2_moe_experts(_ptr(h), hs, _ptr(w_gate), _ptr(w_up), _ptr(w_down), w_gate.stride(0), _act(h, "h"), T, D, F,
+                                  top, cap, _ptr(srt), _ptr(tile_e), _ptr(place), _ptr(wts), _ptr(act), _ptr(rows), _ptr(y), D,
                                   _stream(dev)))
     return y

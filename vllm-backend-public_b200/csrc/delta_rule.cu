@@ -144,18 +144,20 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta,
         v = col_ok ? vcol[(size_t)t * C] : 0.f;
     };
     auto step = [&](int t, const float (&k)[NR], const float (&q)[NR], float g, float be, float v) {
-        float pred = 0.f;
+        float pr[4] = {0.f, 0.f, 0.f, 0.f};            // independent partial sums: the chain is NR / 4 deep
 #pragma unroll
-        for (int m = 0; m < NR; ++m) pred = fmaf(S[m], k[m], pred);
+        for (int m = 0; m < NR; ++m) pr[m & 3] = fmaf(S[m], k[m], pr[m & 3]);
+        float pred = (pr[0] + pr[1]) + (pr[2] + pr[3]);
         pred += __shfl_xor_sync(0xffffffffu, pred, 8);
         pred += __shfl_xor_sync(0xffffffffu, pred, 16);
         const float u = be * (v - g * pred);
-        float acc = 0.f;
+        float ac[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int m = 0; m < NR; ++m) {
             S[m] = fmaf(k[m], u, g * S[m]);
-            acc = fmaf(S[m], q[m], acc);
+            ac[m & 3] = fmaf(S[m], q[m], ac[m & 3]);
         }
+        float acc = (ac[0] + ac[1]) + (ac[2] + ac[3]);
         acc += __shfl_xor_sync(0xffffffffu, acc, 8);
         acc += __shfl_xor_sync(0xffffffffu, acc, 16);
         if (r == 0 && col_ok) ocol[(size_t)t * H * dv] = acc;
@@ -278,19 +280,23 @@ delta_scan_staged_kernel(const float* __restrict__ qkv, const float* __restrict_
             const float v = col_ok ? vs[tt * 32 + jl] : 0.f;
             const float* kt = ks + tt * dk + r;
             const float* qt = qs + tt * dk + r;
-            float pred = 0.f;
+            float kv[NR], pr[4] = {0.f, 0.f, 0.f, 0.f};   // independent partial sums: the chain is NR / 4 deep
 #pragma unroll
-            for (int m = 0; m < NR; ++m) pred = fmaf(S[m], (r + 4 * m < dk) ? kt[4 * m] : 0.f, pred);
+            for (int m = 0; m < NR; ++m) {
+                kv[m] = (r + 4 * m < dk) ? kt[4 * m] : 0.f;
+                pr[m & 3] = fmaf(S[m], kv[m], pr[m & 3]);
+            }
+            float pred = (pr[0] + pr[1]) + (pr[2] + pr[3]);
             pred += __shfl_xor_sync(0xffffffffu, pred, 8);
             pred += __shfl_xor_sync(0xffffffffu, pred, 16);
             const float u = be * (v - g * pred);
-            float acc = 0.f;
+            float ac[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int m = 0; m < NR; ++m) {
-                const bool in = r + 4 * m < dk;
-                S[m] = fmaf(in ? kt[4 * m] : 0.f, u, g * S[m]);
-                acc = fmaf(S[m], in ? qt[4 * m] : 0.f, acc);
+                S[m] = fmaf(kv[m], u, g * S[m]);
+                ac[m & 3] = fmaf(S[m], (r + 4 * m < dk) ? qt[4 * m] : 0.f, ac[m & 3]);
             }
+            float acc = (ac[0] + ac[1]) + (ac[2] + ac[3]);
             acc += __shfl_xor_sync(0xffffffffu, acc, 8);
             acc += __shfl_xor_sync(0xffffffffu, acc, 16);
             if (r == 0 && col_ok) ocol[(size_t)(t0 + tt) * H * dv] = acc;

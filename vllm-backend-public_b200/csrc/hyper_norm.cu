@@ -29,7 +29,8 @@ __global__ void embed_streams_kernel(const T* __restrict__ embed, const int64_t*
     }
 }
 
-template <typename T>
+// MS: compile-time bound on the number of streams (register arrays of MS x 4 values; S <= MS)
+template <typename T, int MS>
 __global__ void __launch_bounds__(512) hc_step_kernel(float* __restrict__ x, int S, int D, const T* __restrict__ y, int64_t y_stride,
                                const float* __restrict__ mix, const float* __restrict__ out_w,
                                const float* __restrict__ in_w, const float* __restrict__ norm_w, float eps, int norm_kind,
@@ -49,9 +50,9 @@ __global__ void __launch_bounds__(512) hc_step_kernel(float* __restrict__ x, int
     // four columns per thread and 16-byte accesses to the streams when the width allows it
     const int W = (D % 4 == 0) ? 4 : 1;
     for (int d = threadIdx.x * W; d < D; d += blockDim.x * W) {
-        float xs[kMaxStreams][4];
+        float xs[MS][4];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) {
+        for (int s = 0; s < MS; ++s) {
             if (s < S) {
                 if (W == 4) {
                     const float4 v = *reinterpret_cast<const float4*>(xt + (size_t)s * D + d);
@@ -67,15 +68,15 @@ __global__ void __launch_bounds__(512) hc_step_kernel(float* __restrict__ x, int
         if (y) {
             float yv[4] = {0.f, 0.f, 0.f, 0.f};
             for (int c = 0; c < W; ++c) yv[c] = b2::ld(y + (size_t)t * y_stride + d + c);
-            float nx[kMaxStreams][4];
+            float nx[MS][4];
 #pragma unroll
-            for (int j = 0; j < kMaxStreams; ++j) {
+            for (int j = 0; j < MS; ++j) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     float a = 0.f;
                     if (j < S) {
 #pragma unroll
-                        for (int s = 0; s < kMaxStreams; ++s)
+                        for (int s = 0; s < MS; ++s)
                             if (s < S) a = fmaf(c_mix[s * S + j], xs[s][c], a);
                         a = fmaf(c_out[j], yv[c], a);
                     }
@@ -87,7 +88,7 @@ __global__ void __launch_bounds__(512) hc_step_kernel(float* __restrict__ x, int
                 }
             }
 #pragma unroll
-            for (int j = 0; j < kMaxStreams; ++j)
+            for (int j = 0; j < MS; ++j)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) xs[j][c] = nx[j][c];
         }
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(512) hc_step_kernel(float* __restrict__ x, int
             for (int c = 0; c < W; ++c) {
                 float u = 0.f;
 #pragma unroll
-                for (int s = 0; s < kMaxStreams; ++s)
+                for (int s = 0; s < MS; ++s)
                     if (s < S) u = fmaf(c_in[s], xs[s][c], u);
                 u_sm[d + c] = u;
                 sum += u;
@@ -140,13 +141,21 @@ extern "C" int b2_hc_step(float* x, int T, int S, int D, const void* y, int64_t 
     const size_t smem = h ? (size_t)D * sizeof(float) : 0;
     B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "hc_step: width %d does not fit shared memory", D);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int threads = D >= 1024 ? 512 : 256;
+    const int threads = D >= 4096 ? 512 : 256;
+#define B2_HC(MS)                                                                                                          \
+    do {                                                                                                                   \
+        auto kern = hc_step_kernel<A, MS>;                                                                                 \
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        kern<<<T, threads, smem, st>>>(x, S, D, static_cast<const A*>(y), y_stride, mix, out_w, in_w, norm_w, eps, norm_kind, \
+                                       static_cast<A*>(h), h_stride);                                                      \
+    } while (0)
     B2_DISPATCH_ACT(act_dtype, A, {
-        auto kern = hc_step_kernel<A>;
-        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<T, threads, smem, st>>>(x, S, D, static_cast<const A*>(y), y_stride, mix, out_w, in_w, norm_w, eps, norm_kind,
-                                       static_cast<A*>(h), h_stride);
+        if (S == 1) B2_HC(1);
+        else if (S == 2) B2_HC(2);
+        else if (S <= 4) B2_HC(4);
+        else B2_HC(8);
     });
+#undef B2_HC
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }

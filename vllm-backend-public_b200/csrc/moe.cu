@@ -80,7 +80,8 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, cons
 
 // ------------------------------------------------------------------------------------------------- align
 __global__ void moe_align_kernel(const int32_t* __restrict__ ids, int n, int E, int cap, int32_t* __restrict__ sorted,
-                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ place) {
+                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ place,
+                                 int32_t* __restrict__ group_ends) {
     extern __shared__ int sm[];                      // counts [E] | offs [E] | fill [E]
     int* counts = sm;
     int* offs = sm + E;
@@ -104,6 +105,8 @@ __global__ void moe_align_kernel(const int32_t* __restrict__ ids, int n, int E, 
     }
     __syncthreads();
     const int tiles = cap / kMoeBM;
+    if (group_ends)                                  // row where expert e's (padded) group ends: offsets of a grouped GEMM
+        for (int e = threadIdx.x; e < E; e += blockDim.x) group_ends[e] = e + 1 < E ? offs[e + 1] : total;
     for (int e = threadIdx.x; e < E; e += blockDim.x)
         for (int t = offs[e] / kMoeBM; t < (offs[e] + counts[e] + kMoeBM - 1) / kMoeBM; ++t) tile_expert[t] = e;
     for (int t = total / kMoeBM + threadIdx.x; t < tiles; t += blockDim.x) tile_expert[t] = -1;
@@ -235,8 +238,8 @@ __device__ __forceinline__ void tile_product(FA a_row, FB0 b0_row, FB1 b1_row, i
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_gate, const T* __restrict__ w_up,
-                   const int32_t* __restrict__ sorted, const int32_t* __restrict__ tile_expert, int top, int D, int F,
-                   bool vec, T* __restrict__ act) {
+                   int64_t w13_expert_stride, const int32_t* __restrict__ sorted, const int32_t* __restrict__ tile_expert,
+                   int top, int D, int F, bool vec, T* __restrict__ act) {
     constexpr int LD = kMoeBK + Pad<T>::v;
     __shared__ __align__(32) T a_sm[kMoeBM * LD];
     __shared__ __align__(32) T b_sm[2 * kMoeBN * LD];
@@ -244,8 +247,8 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restric
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
     const int m0 = blockIdx.x * kMoeBM, n0 = blockIdx.y * kMoeBN;
-    const T* wg = w_gate + (size_t)e * F * D;
-    const T* wu = w_up + (size_t)e * F * D;
+    const T* wg = w_gate + (size_t)e * w13_expert_stride;
+    const T* wu = w_up + (size_t)e * w13_expert_stride;
     auto a_row = [&](int r) -> const T* {
         const int s = sorted[m0 + r];
         return s >= 0 ? h + (size_t)(s / top) * h_stride : nullptr;
@@ -283,15 +286,31 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
     }
 }
 
+// out[p] = h[token of sorted[p]] for the rows of the sorted list, zeros for padding rows: the A operand of a grouped GEMM
 template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ place,
+__global__ void moe_gather_kernel(const T* __restrict__ h, int64_t h_stride, const int32_t* __restrict__ sorted, int top,
+                                  int D, bool vec, T* __restrict__ out) {
+    const int p = blockIdx.x, s = sorted[p];
+    const T* src = s >= 0 ? h + (size_t)(s / top) * h_stride : nullptr;
+    T* dst = out + (size_t)p * D;
+    if (vec) {
+        constexpr int VE = 16 / sizeof(T);
+        for (int i = threadIdx.x * VE; i < D; i += blockDim.x * VE)
+            *reinterpret_cast<uint4*>(dst + i) = src ? *reinterpret_cast<const uint4*>(src + i) : make_uint4(0, 0, 0, 0);
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src ? src[i] : T(0.f);
+    }
+}
+
+template <typename T, typename R>
+__global__ void moe_combine_kernel(const R* __restrict__ rows, const int32_t* __restrict__ place,
                                    const float* __restrict__ wts, int top, int D, T* __restrict__ y, int64_t y_stride) {
     const int t = blockIdx.x;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float a = 0.f;
         for (int j = 0; j < top; ++j) {
             const int p = place[(size_t)t * top + j];
-            if (p >= 0) a = fmaf(wts[(size_t)t * top + j], rows[(size_t)p * D + d], a);
+            if (p >= 0) a = fmaf(wts[(size_t)t * top + j], b2::ld(rows + (size_t)p * D + d), a);
         }
         b2::st(y + (size_t)t * y_stride + d, a);
     }
@@ -327,20 +346,21 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
 }
 
 extern "C" int b2_moe_align(const int32_t* ids, int n, int E, int cap, int32_t* sorted, int32_t* tile_expert, int32_t* place,
-                            void* stream) {
+                            int32_t* group_ends, void* stream) {
     B2_REQUIRE(n >= 0 && E > 0 && cap % kMoeBM == 0 && cap >= b2_moe_capacity(n, E), B2_EINVAL,
                "moe_align: capacity %d below %d for %d rows over %d experts", cap, b2_moe_capacity(n, E), n, E);
     if (n == 0) return B2_OK;
     B2_REQUIRE(ids && sorted && tile_expert && place, B2_EINVAL, "moe_align: null pointer");
     const size_t smem = (size_t)3 * E * sizeof(int);
     B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "moe_align: %d experts do not fit shared memory", E);
-    moe_align_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(ids, n, E, cap, sorted, tile_expert, place);
+    moe_align_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(ids, n, E, cap, sorted, tile_expert, place, group_ends);
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
 
 extern "C" int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gate, const void* w_up, const void* w_down,
-                              int act_dtype, int T, int D, int F, int top, int cap, const int32_t* sorted,
+                              int64_t w13_expert_stride, int act_dtype, int T, int D, int F, int top, int cap,
+                              const int32_t* sorted,
                               const int32_t* tile_expert, const int32_t* place, const float* weights, void* act, float* rows,
                               void* y, int64_t y_stride, void* stream) {
     B2_REQUIRE(T >= 0 && D > 0 && F > 0 && top >= 1 && cap % kMoeBM == 0, B2_EINVAL, "moe_experts: bad sizes");
@@ -350,15 +370,48 @@ extern "C" int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gat
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int tiles = cap / kMoeBM;
     const int ve = act_dtype == B2_ACT_BF16 ? 8 : 4;
-    const bool vec1 = D % ve == 0 && h_stride % ve == 0 && b2_aligned16(h) && b2_aligned16(w_gate) && b2_aligned16(w_up);
+    B2_REQUIRE(w13_expert_stride >= (int64_t)F * D, B2_EINVAL, "moe_experts: expert stride below F*D");
+    const bool vec1 = D % ve == 0 && h_stride % ve == 0 && w13_expert_stride % ve == 0 && b2_aligned16(h) &&
+                      b2_aligned16(w_gate) && b2_aligned16(w_up);
     const bool vec2 = F % ve == 0 && b2_aligned16(act) && b2_aligned16(w_down);
     B2_DISPATCH_ACT(act_dtype, A, {
         moe_gate_up_kernel<A><<<dim3(tiles, (F + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
-            static_cast<const A*>(h), h_stride, static_cast<const A*>(w_gate), static_cast<const A*>(w_up), sorted, tile_expert,
-            top, D, F, vec1, static_cast<A*>(act));
+            static_cast<const A*>(h), h_stride, static_cast<const A*>(w_gate), static_cast<const A*>(w_up), w13_expert_stride,
+            sorted, tile_expert, top, D, F, vec1, static_cast<A*>(act));
         moe_down_kernel<A><<<dim3(tiles, (D + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
             static_cast<const A*>(act), static_cast<const A*>(w_down), sorted, tile_expert, D, F, vec2, rows);
-        moe_combine_kernel<A><<<T, 256, 0, st>>>(rows, place, weights, top, D, static_cast<A*>(y), y_stride);
+        moe_combine_kernel<A, float><<<T, 256, 0, st>>>(rows, place, weights, top, D, static_cast<A*>(y), y_stride);
+    });
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_moe_gather(const void* h, int64_t h_stride, int act_dtype, const int32_t* sorted, int cap, int top, int D,
+                             void* out, void* stream) {
+    B2_REQUIRE(cap >= 0 && top >= 1 && D > 0, B2_EINVAL, "moe_gather: bad sizes");
+    if (cap == 0) return B2_OK;
+    B2_REQUIRE(h && sorted && out, B2_EINVAL, "moe_gather: null pointer");
+    const int ve = act_dtype == B2_ACT_BF16 ? 8 : 4;
+    const bool vec = D % ve == 0 && h_stride % ve == 0 && b2_aligned16(h) && b2_aligned16(out);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, (moe_gather_kernel<A><<<cap, 128, 0, st>>>(static_cast<const A*>(h), h_stride, sorted, top, D, vec,
+                                                                           static_cast<A*>(out))));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+// y[t] = sum_j weights[t, j] * rows[place[t, j]] in fp32, choice order; rows in the activation type (rows_f32 = 0) or fp32
+extern "C" int b2_moe_combine(const void* rows, int rows_f32, const int32_t* place, const float* weights, int T, int top, int D,
+                              void* y, int64_t y_stride, int act_dtype, void* stream) {
+    B2_REQUIRE(T >= 0 && top >= 1 && D > 0, B2_EINVAL, "moe_combine: bad sizes");
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(rows && place && weights && y, B2_EINVAL, "moe_combine: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        if (rows_f32) moe_combine_kernel<A, float><<<T, 256, 0, st>>>(static_cast<const float*>(rows), place, weights, top, D,
+                                                                      static_cast<A*>(y), y_stride);
+        else moe_combine_kernel<A, A><<<T, 256, 0, st>>>(static_cast<const A*>(rows), place, weights, top, D, static_cast<A*>(y),
+                                                         y_stride);
     });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
