@@ -159,19 +159,21 @@ def _kernels(size, s, B, ctx, T):
         # ---- experts  |  like: the dense gated feed-forward of equal active width (two cuBLAS GEMMs + silu_and_mul)
         h = torch.randn(rows, D, device=dev).to(bf)
         wr, rb = (torch.randn(E, D, device=dev) * D ** -0.5).to(bf), torch.zeros(E, device=dev)
-        wg, wu = (torch.randn(E, F, D, device=dev) * D ** -0.5).to(bf), (torch.randn(E, F, D, device=dev) * D ** -0.5).to(bf)
+        wgu = (torch.randn(E, 2 * F, D, device=dev) * D ** -0.5).to(bf)
+        wg, wu = wgu[:, :F], wgu[:, F:]
         wd = (torch.randn(E, D, F, device=dev) * F ** -0.5).to(bf)
         ms = _time(lambda: ops.moe_route(h, wr, rb, top), flush)
         line("moe_route", phase, ms, bytes_=rows * D * 2 + E * D * 2, flops=2 * rows * E * D)
         ids, wts = ops.moe_route(h, wr, rb, top)
-        ms = _time(lambda: ops.moe_experts(h, ids, wts, wg, wu, wd), flush)
+        ms = _time(lambda: ops.moe_experts(h, ids, wts, wg, wu, wd, w_gate_up=wgu), flush)
         used = min(E, rows * top)
-        line("moe_experts (align + 2 grouped products + combine)", phase, ms, bytes_=used * 3 * F * D * 2,
+        path = "vendor grouped GEMM" if rows * top >= ops.MOE_GROUPED_GEMM_MIN_PAIRS else "own tiled kernels"
+        line(f"moe_experts (sort + 2 grouped products + combine; {path})", phase, ms, bytes_=used * 3 * F * D * 2,
              flops=6 * rows * top * F * D, like="dense gated MLP")
         w1, w2 = (torch.randn(2 * top * F, D, device=dev) * D ** -0.5).to(bf), (torch.randn(D, top * F, device=dev) * 0.02).to(bf)
         ms = _time(lambda: torch.nn.functional.linear(ops.silu_and_mul(torch.nn.functional.linear(h, w1)), w2), flush)
         line("dense gated MLP (Llama: cuBLAS + silu_and_mul)", phase, ms, bytes_=3 * top * F * D * 2, flops=6 * rows * top * F * D)
-        del wg, wu, wd, w1, w2, kc, vc, state
+        del wg, wu, wgu, wd, w1, w2, kc, vc, state
         torch.cuda.empty_cache()
 
 
@@ -181,7 +183,7 @@ def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
     from b200attn.model import ModelConfig
     if family != "kofadra":
         raise SystemExit(f"unknown family {family!r}")
-    B, ctx, T = 64, 2048, 4096
+    B, ctx, T = 64, 2560, 4096          # ctx: 2.5 mask blocks of the bench geometry, so a decode row sees 513 keys
     for name in sizes:
         s = SIZES[name]
         kcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"], s["top"],

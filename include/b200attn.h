@@ -487,8 +487,8 @@ B2_API int b2_delta_prep(const void* proj, int64_t proj_stride, int off_b, int o
                          const float* dt_bias, const int32_t* cu_q, const int32_t* ctx_start,
                          const int32_t* state_slot, int n_seq, void* conv_state, float* qkv, float* beta, float* decay,
                          void* stream);
-B2_API int b2_delta_scan(const float* qkv, const float* beta, const float* decay, int H, int G, int dk, int dv,
-                         const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
+B2_API int b2_delta_scan(const float* qkv, const float* beta, const float* decay, int total_rows, int H, int G, int dk,
+                         int dv, const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
                          float* state, float* o, void* stream);
 B2_API int b2_delta_out(const float* o, const void* proj, int64_t proj_stride, int off_g, int act_dtype, int T, int H,
                         int dv, const float* norm_w, float eps, void* out, int64_t out_stride, void* stream);

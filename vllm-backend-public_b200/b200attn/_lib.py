@@ -107,7 +107,7 @@ SIGNATURES = {
     "b2_hc_step": (i32, [vp, i32, i32, i32, vp, i64, vp, vp, vp, vp, f32, i32, vp, i64, i32, vp]),
     "b2_delta_prep": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp,
                             vp, vp]),
-    "b2_delta_scan": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, i32, vp, vp, vp]),
+    "b2_delta_scan": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, i32, vp, vp, vp]),
     "b2_delta_out": (i32, [vp, vp, i64, i32, i32, i32, i32, i32, vp, f32, vp, i64, vp]),
     "b2_qknorm_cache": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, vp, vp, f32, vp, i32, vp, vp, vp, vp]),
     "b2_chunk_attention": (i32, [vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, f32,

@@ -763,7 +763,7 @@ def delta_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, H: in
     if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, dk, dv):
         raise ValueError(f"state must be contiguous fp32 [slots, {H}, {dk}, {dv}]")
     o = torch.empty(T, H, dv, dtype=torch.float32, device=dev)
-    _lib.check(lib.b2_delta_scan(_ptr(qkv), _ptr(beta), _ptr(decay), H, G, dk, dv, _ptr(batch.cu_q), _ptr(batch.ctx_start),
+    _lib.check(lib.b2_delta_scan(_ptr(qkv), _ptr(beta), _ptr(decay), T, H, G, dk, dv, _ptr(batch.cu_q), _ptr(batch.ctx_start),
                                  _ptr(batch.state_slots), batch.n_seq, _ptr(state), _ptr(o), _stream(dev)))
     return o
 

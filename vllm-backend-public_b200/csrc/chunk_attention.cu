@@ -133,6 +133,167 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
     }
 }
 
+// ------------------------------------------------------------------------------------------------- grouped decode kernel
+// bf16 rows that the tiled kernel does not take (decode rows, short portions): one CTA per (row, kv head) serves ALL the
+// query heads of that kv head, so K and V are read once per group instead of once per head.  Four warps share the visible
+// keys 32 at a time (a lane per key, 16-byte loads of its K row, one dot product per query head), keep an online softmax
+// per head, accumulate P.V with a lane per pair of value columns, and merge through shared memory; the sink enters
+// through warp 0's initial state.  Up to kGroupMaxHeads query heads per pass (more: further passes over the keys).
+constexpr int kGroupMaxHeads = 8, kGroupMaxPairs = 4;      // dv <= 256
+
+__global__ void __launch_bounds__(128)
+chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                             const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_tables, int max_nb,
+                             const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start, int n_seq, int H, int G,
+                             int dk, int dv, int bs, float scale, int chunk, float sink, float sink_logit, int skip_rows_from,
+                             __nv_bfloat16* __restrict__ out) {
+    extern __shared__ __align__(16) float grp_sm[];        // q [QH][dk] | per warp: m [QH], l [QH], acc [QH][dv]
+    const int row = blockIdx.x, g = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int seq = b2::seq_of_row(cu_q, n_seq, row);
+    const int ctx = ctx_start[seq];
+    const int QHall = H / G;
+    if (skip_rows_from > 0 && ctx >= 0 && cu_q[seq + 1] - cu_q[seq] >= skip_rows_from) return;    // the tile kernel's
+    if (ctx < 0) {
+        for (int i = tid; i < QHall * dv; i += 128) out[((size_t)row * H + (size_t)g * QHall) * dv + i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int pos = ctx + row - cu_q[seq];
+    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    const int32_t* bt = block_tables + (size_t)seq * max_nb;
+    const int npairs = dv / 2;
+    for (int h0 = 0; h0 < QHall; h0 += kGroupMaxHeads) {
+        const int QH = min(kGroupMaxHeads, QHall - h0);
+        float* qs = grp_sm;
+        float* part = grp_sm + kGroupMaxHeads * dk;
+        __syncthreads();                                   // a previous pass is done with the shared memory
+        for (int i = tid; i < QH * dk; i += 128)
+            qs[i] = __bfloat162float(q[((size_t)row * H + (size_t)g * QHall + h0) * dk + i]) * scale;
+        __syncthreads();
+        float m[kGroupMaxHeads], l[kGroupMaxHeads], acc[kGroupMaxHeads][kGroupMaxPairs][2];
+#pragma unroll
+        for (int h = 0; h < kGroupMaxHeads; ++h) {
+            m[h] = (w == 0 && sink > 0.f) ? sink_logit : -INFINITY;
+            l[h] = w == 0 ? sink : 0.f;
+#pragma unroll
+            for (int c = 0; c < kGroupMaxPairs; ++c) acc[h][c][0] = acc[h][c][1] = 0.f;
+        }
+        for (int j0 = lo + w * 32; j0 <= pos; j0 += 128) {
+            const int j = j0 + lane;
+            const bool valid = j <= pos;
+            float sc[kGroupMaxHeads];
+#pragma unroll
+            for (int h = 0; h < kGroupMaxHeads; ++h) sc[h] = 0.f;
+            size_t vbase = 0;
+            if (valid) {
+                const size_t tile = ((size_t)bt[j / bs] * G + g) * bs + (j % bs);
+                const __nv_bfloat16* kr = k_cache + tile * dk;
+                vbase = tile * dv;
+                for (int c = 0; c < dk; c += 8) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
+                    const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+                    float kf[8];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        kf[2 * e] = __uint_as_float(wds[e] << 16);
+                        kf[2 * e + 1] = __uint_as_float(wds[e] & 0xffff0000u);
+                    }
+#pragma unroll
+                    for (int h = 0; h < kGroupMaxHeads; ++h) {
+                        if (h < QH) {
+                            const float4 qa = *reinterpret_cast<const float4*>(qs + h * dk + c);
+                            const float4 qb = *reinterpret_cast<const float4*>(qs + h * dk + c + 4);
+                            sc[h] = fmaf(qa.x, kf[0], sc[h]); sc[h] = fmaf(qa.y, kf[1], sc[h]);
+                            sc[h] = fmaf(qa.z, kf[2], sc[h]); sc[h] = fmaf(qa.w, kf[3], sc[h]);
+                            sc[h] = fmaf(qb.x, kf[4], sc[h]); sc[h] = fmaf(qb.y, kf[5], sc[h]);
+                            sc[h] = fmaf(qb.z, kf[6], sc[h]); sc[h] = fmaf(qb.w, kf[7], sc[h]);
+                        }
+                    }
+                }
+            }
+            float pr[kGroupMaxHeads];
+#pragma unroll
+            for (int h = 0; h < kGroupMaxHeads; ++h) {
+                pr[h] = 0.f;
+                if (h < QH) {
+                    const float x = valid ? sc[h] : -INFINITY;
+                    const float mn = fmaxf(m[h], b2::warp_max(x));          // finite: the tile has at least one key
+                    const float corr = m[h] == -INFINITY ? 0.f : __expf(m[h] - mn);
+                    pr[h] = valid ? __expf(x - mn) : 0.f;
+                    l[h] = l[h] * corr + b2::warp_sum(pr[h]);
+                    m[h] = mn;
+#pragma unroll
+                    for (int c = 0; c < kGroupMaxPairs; ++c) {
+                        acc[h][c][0] *= corr;
+                        acc[h][c][1] *= corr;
+                    }
+                }
+            }
+            const int nk = min(32, pos - j0 + 1);
+            for (int kk = 0; kk < nk; ++kk) {
+                const size_t vb = __shfl_sync(0xffffffffu, (unsigned long long)vbase, kk);
+                float vx[kGroupMaxPairs], vy[kGroupMaxPairs];
+#pragma unroll
+                for (int c = 0; c < kGroupMaxPairs; ++c) {
+                    const int pi = lane + 32 * c;
+                    vx[c] = vy[c] = 0.f;
+                    if (pi < npairs) {
+                        const uint32_t wd = *reinterpret_cast<const uint32_t*>(v_cache + vb + 2 * pi);
+                        vx[c] = __uint_as_float(wd << 16);
+                        vy[c] = __uint_as_float(wd & 0xffff0000u);
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < kGroupMaxHeads; ++h) {
+                    if (h < QH) {
+                        const float ph = __shfl_sync(0xffffffffu, pr[h], kk);
+#pragma unroll
+                        for (int c = 0; c < kGroupMaxPairs; ++c) {
+                            acc[h][c][0] = fmaf(ph, vx[c], acc[h][c][0]);
+                            acc[h][c][1] = fmaf(ph, vy[c], acc[h][c][1]);
+                        }
+                    }
+                }
+            }
+        }
+        // merge the four warps
+        float* mine = part + (size_t)w * kGroupMaxHeads * (2 + dv);
+#pragma unroll
+        for (int h = 0; h < kGroupMaxHeads; ++h) {
+            if (h < QH) {
+                if (lane == 0) {
+                    mine[h * (2 + dv)] = m[h];
+                    mine[h * (2 + dv) + 1] = l[h];
+                }
+#pragma unroll
+                for (int c = 0; c < kGroupMaxPairs; ++c) {
+                    const int pi = lane + 32 * c;
+                    if (pi < npairs) {
+                        mine[h * (2 + dv) + 2 + 2 * pi] = acc[h][c][0];
+                        mine[h * (2 + dv) + 3 + 2 * pi] = acc[h][c][1];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < QH * dv; i += 128) {
+            const int h = i / dv, col = i % dv;
+            float M = -INFINITY;
+            for (int x = 0; x < 4; ++x) M = fmaxf(M, part[((size_t)x * kGroupMaxHeads + h) * (2 + dv)]);
+            float L = 0.f, O = 0.f;
+            if (M > -INFINITY) {
+                for (int x = 0; x < 4; ++x) {
+                    const float* px = part + ((size_t)x * kGroupMaxHeads + h) * (2 + dv);
+                    const float f = px[0] == -INFINITY ? 0.f : __expf(px[0] - M);
+                    L = fmaf(px[1], f, L);
+                    O = fmaf(px[2 + col], f, O);
+                }
+            }
+            out[((size_t)row * H + (size_t)g * QHall + h0 + h) * dv + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------- tiled prompt kernel
 // bf16, dk and dv multiples of 16: one CTA = 64 consecutive query rows of one sequence x one head, four warps of 16 rows.
 // Keys are walked 64 at a time from the first row's block start to the last row's position (at most chunk + 63 keys
@@ -362,6 +523,20 @@ extern "C" int b2_chunk_attention(void* out, const void* q, const void* k_cache,
         B2_TILE(6, 2) B2_TILE(6, 4) B2_TILE(6, 6) B2_TILE(6, 8) B2_TILE(8, 2) B2_TILE(8, 4) B2_TILE(8, 6) B2_TILE(8, 8)
 #undef B2_TILE
         if (rc != B2_OK) return rc;
+    }
+    if (act_dtype == B2_ACT_BF16 && dk % 8 == 0 && dv % 2 == 0 && dv <= 64 * kGroupMaxPairs && b2_aligned16(q) &&
+        b2_aligned16(k_cache) && b2_aligned16(v_cache) && b2_aligned16(out)) {
+        const size_t gsm = (size_t)(kGroupMaxHeads * dk + 4 * kGroupMaxHeads * (2 + dv)) * sizeof(float);
+        if (gsm <= 96 * 1024) {
+            auto kern = chunk_attention_group_kernel;
+            if (gsm > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm));
+            kern<<<dim3(T, G), 128, gsm, st>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
+                                               static_cast<const __nv_bfloat16*>(v_cache), block_tables, max_nb, cu_q, ctx_start,
+                                               n_seq, H, G, dk, dv, bs, scale, chunk, sink, sink_logit, skip_from,
+                                               static_cast<__nv_bfloat16*>(out));
+            B2_CUDA_OK(cudaGetLastError());
+            return B2_OK;
+        }
     }
     B2_DISPATCH_ACT(act_dtype, A, (chunk_attention_kernel<A><<<blocks, warps * 32, smem, st>>>(
         static_cast<const A*>(q), static_cast<const A*>(k_cache), static_cast<const A*>(v_cache), block_tables, max_nb, cu_q,

@@ -200,33 +200,41 @@ __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(b2::smem_u32(dst)), "l"(src) : "memory");
 }
 
-template <int NR, int TT>
+// R lanes share a column of S (R = 4: eight columns a warp, full 32-byte sectors when the state streams through in a
+// decode step; R = 8: four columns a warp, half the work per lane on the per-token chain of a long chunk).  A lane owns
+// the NR consecutive rows r*NR .. r*NR+NR-1, so its k and q values are 16-byte shared-memory reads; rows of the staged
+// k / q are padded by four floats per lane group to spread the banks.  FULL: dk == R*NR, no row predicates.
+template <int NR, int R, int TT, bool FULL>
 __global__ void __launch_bounds__(128)
 delta_scan_staged_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                          int H, int G, int dk, int dv, const int32_t* __restrict__ cu_q,
                          const int32_t* __restrict__ ctx_start, const int32_t* __restrict__ state_slot,
                          float* __restrict__ state, float* __restrict__ o) {
+    constexpr int CW = 32 / R;                       // columns per warp
+    constexpr int CB = 4 * CW;                       // columns per CTA
+    constexpr int LDR = NR + 4;                      // padded row group
+    constexpr int KQ = R * LDR;                      // floats of one token's staged k (or q)
     extern __shared__ __align__(16) float scan_sm[];
     const int seq = blockIdx.x, hh = blockIdx.y;
     const int ctx = ctx_start[seq];
     if (ctx < 0) return;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int r = lane >> 3, jj = lane & 7;
-    const int j0 = blockIdx.z * 32;
-    const int jl = wid * 8 + jj, j = j0 + jl;        // column of S (local, global)
+    const int r = lane / CW, jj = lane % CW;
+    const int j0 = blockIdx.z * CB;
+    const int jl = wid * CW + jj, j = j0 + jl;       // column of S (local, global)
     const bool col_ok = j < dv;
     const int slot = state_slot[seq];
     const int C = 2 * G * dk + H * dv;
     const int kvh = hh / (H / G);
     const int r0 = cu_q[seq], n = cu_q[seq + 1] - r0;
-    // stage layout: k [TT][dk] | q [TT][dk] | v [TT][32] | decay [TT] | beta [TT]
-    const int stage_floats = TT * (2 * dk + 32 + 2);
+    // stage layout: k [TT][KQ] | q [TT][KQ] | v [TT][CB] | decay [TT] | beta [TT]
+    constexpr int stage_floats = TT * (2 * KQ + CB + 2);
     float S[NR];
     float* sp = slot >= 0 ? state + ((size_t)slot * H + hh) * dk * dv : nullptr;
 #pragma unroll
     for (int m = 0; m < NR; ++m) {
-        const int i = r + 4 * m;
-        S[m] = (sp && ctx > 0 && col_ok && i < dk) ? sp[(size_t)i * dv + j] : 0.f;
+        const int i = r * NR + m;
+        S[m] = (sp && ctx > 0 && col_ok && (FULL || i < dk)) ? sp[(size_t)i * dv + j] : 0.f;
     }
     const float* qrow = qkv + (size_t)r0 * C + (size_t)kvh * dk;
     const float* krow = qrow + (size_t)G * dk;
@@ -234,23 +242,24 @@ delta_scan_staged_kernel(const float* __restrict__ qkv, const float* __restrict_
     const float* grow = decay + (size_t)r0 * H + hh;
     const float* brow = beta + (size_t)r0 * H + hh;
     float* ocol = o + ((size_t)r0 * H + hh) * dv + (col_ok ? j : 0);
-    const int vcols = min(32, dv - j0);              // a multiple of 4
+    const int vcols = min(CB, dv - j0);              // a multiple of 4
     auto issue = [&](int tile, int buf) {
         float* ks = scan_sm + (size_t)buf * stage_floats;
-        float* qs = ks + TT * dk;
-        float* vs = qs + TT * dk;
-        float* gs = vs + TT * 32;
+        float* qs = ks + TT * KQ;
+        float* vs = qs + TT * KQ;
+        float* gs = vs + TT * CB;
         float* bs_ = gs + TT;
         const int t0 = tile * TT, nt = min(TT, n - t0);
         const int per = dk / 4;
         for (int idx = tid; idx < nt * per; idx += 128) {
             const int tt = idx / per, c = (idx % per) * 4;
-            cp_async16(ks + tt * dk + c, krow + (size_t)(t0 + tt) * C + c);
-            cp_async16(qs + tt * dk + c, qrow + (size_t)(t0 + tt) * C + c);
+            const int dst = tt * KQ + (c / NR) * LDR + c % NR;
+            cp_async16(ks + dst, krow + (size_t)(t0 + tt) * C + c);
+            cp_async16(qs + dst, qrow + (size_t)(t0 + tt) * C + c);
         }
-        for (int idx = tid; idx < nt * 8; idx += 128) {
-            const int tt = idx >> 3, c = (idx & 7) * 4;
-            if (c < vcols) cp_async16(vs + tt * 32 + c, vrow + (size_t)(t0 + tt) * C + c);
+        for (int idx = tid; idx < nt * (CB / 4); idx += 128) {
+            const int tt = idx / (CB / 4), c = (idx % (CB / 4)) * 4;
+            if (c < vcols) cp_async16(vs + tt * CB + c, vrow + (size_t)(t0 + tt) * C + c);
         }
         if (tid < nt) {
             cp_async4(gs + tid, grow + (size_t)(t0 + tid) * H);
@@ -270,35 +279,43 @@ delta_scan_staged_kernel(const float* __restrict__ qkv, const float* __restrict_
         }
         __syncthreads();
         const float* ks = scan_sm + (size_t)buf * stage_floats;
-        const float* qs = ks + TT * dk;
-        const float* vs = qs + TT * dk;
-        const float* gs = vs + TT * 32;
+        const float* qs = ks + TT * KQ;
+        const float* vs = qs + TT * KQ;
+        const float* gs = vs + TT * CB;
         const float* bs_ = gs + TT;
         const int t0 = tile * TT, nt = min(TT, n - t0);
         for (int tt = 0; tt < nt; ++tt) {
             const float g = gs[tt], be = bs_[tt];
-            const float v = col_ok ? vs[tt * 32 + jl] : 0.f;
-            const float* kt = ks + tt * dk + r;
-            const float* qt = qs + tt * dk + r;
-            float kv[NR], pr[4] = {0.f, 0.f, 0.f, 0.f};   // independent partial sums: the chain is NR / 4 deep
+            const float v = col_ok ? vs[tt * CB + jl] : 0.f;
+            float kv[NR], qv[NR];
 #pragma unroll
-            for (int m = 0; m < NR; ++m) {
-                kv[m] = (r + 4 * m < dk) ? kt[4 * m] : 0.f;
-                pr[m & 3] = fmaf(S[m], kv[m], pr[m & 3]);
+            for (int m = 0; m < NR; m += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(ks + tt * KQ + r * LDR + m);
+                const float4 c = *reinterpret_cast<const float4*>(qs + tt * KQ + r * LDR + m);
+                kv[m] = a.x; kv[m + 1] = a.y; kv[m + 2] = a.z; kv[m + 3] = a.w;
+                qv[m] = c.x; qv[m + 1] = c.y; qv[m + 2] = c.z; qv[m + 3] = c.w;
             }
+            if (!FULL) {
+#pragma unroll
+                for (int m = 0; m < NR; ++m)
+                    if (r * NR + m >= dk) kv[m] = qv[m] = 0.f;      // rows past dk: stale shared memory
+            }
+            float pr[4] = {0.f, 0.f, 0.f, 0.f};      // independent partial sums: the chain is NR / 4 deep
+#pragma unroll
+            for (int m = 0; m < NR; ++m) pr[m & 3] = fmaf(S[m], kv[m], pr[m & 3]);
             float pred = (pr[0] + pr[1]) + (pr[2] + pr[3]);
-            pred += __shfl_xor_sync(0xffffffffu, pred, 8);
-            pred += __shfl_xor_sync(0xffffffffu, pred, 16);
+#pragma unroll
+            for (int x = CW; x < 32; x <<= 1) pred += __shfl_xor_sync(0xffffffffu, pred, x);
             const float u = be * (v - g * pred);
             float ac[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int m = 0; m < NR; ++m) {
                 S[m] = fmaf(kv[m], u, g * S[m]);
-                ac[m & 3] = fmaf(S[m], (r + 4 * m < dk) ? qt[4 * m] : 0.f, ac[m & 3]);
+                ac[m & 3] = fmaf(S[m], qv[m], ac[m & 3]);
             }
             float acc = (ac[0] + ac[1]) + (ac[2] + ac[3]);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+#pragma unroll
+            for (int x = CW; x < 32; x <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
             if (r == 0 && col_ok) ocol[(size_t)(t0 + tt) * H * dv] = acc;
         }
         __syncthreads();                             // the stage is free for the tile after next
@@ -306,8 +323,8 @@ delta_scan_staged_kernel(const float* __restrict__ qkv, const float* __restrict_
     if (sp && col_ok) {
 #pragma unroll
         for (int m = 0; m < NR; ++m) {
-            const int i = r + 4 * m;
-            if (i < dk) sp[(size_t)i * dv + j] = S[m];
+            const int i = r * NR + m;
+            if (FULL || i < dk) sp[(size_t)i * dv + j] = S[m];
         }
     }
 }
@@ -363,31 +380,51 @@ extern "C" int b2_delta_prep(const void* proj, int64_t proj_stride, int off_b, i
     return B2_OK;
 }
 
-extern "C" int b2_delta_scan(const float* qkv, const float* beta, const float* decay, int H, int G, int dk, int dv,
-                             const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
+extern "C" int b2_delta_scan(const float* qkv, const float* beta, const float* decay, int total_rows, int H, int G, int dk,
+                             int dv, const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
                              float* state, float* o, void* stream) {
     B2_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, B2_EINVAL, "delta_scan: bad sizes");
     B2_REQUIRE(dk <= 256, B2_EUNSUPPORTED, "delta_scan: key size %d above 256", dk);
     if (n_seq == 0) return B2_OK;
     B2_REQUIRE(qkv && beta && decay && cu_q && ctx_start && state_slot && state && o, B2_EINVAL, "delta_scan: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const dim3 grid(n_seq, H, (dv + 31) / 32);
     const bool staged = dk % 4 == 0 && dv % 4 == 0 && b2_aligned16(qkv);       // rows of 2*G*dk + H*dv floats stay aligned
-#define B2_SCAN(NR, TT)                                                                                                    \
+    if (!staged) {
+        const dim3 grid(n_seq, H, (dv + 31) / 32);
+        if (dk <= 32) delta_scan_kernel<8><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
+        else if (dk <= 64) delta_scan_kernel<16><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
+        else if (dk <= 128) delta_scan_kernel<32><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
+        else delta_scan_kernel<64><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
+        B2_CUDA_OK(cudaGetLastError());
+        return B2_OK;
+    }
+#define B2_SCAN(NR, R, TT)                                                                                                 \
     do {                                                                                                                   \
-        if (staged) {                                                                                                      \
-            const size_t smem = (size_t)2 * TT * (2 * dk + 32 + 2) * sizeof(float);                                        \
-            auto kern = delta_scan_staged_kernel<NR, TT>;                                                                  \
+        const dim3 grid(n_seq, H, (dv + 128 / R - 1) / (128 / R));                                                         \
+        const size_t smem = (size_t)2 * TT * (2 * R * (NR + 4) + 128 / R + 2) * sizeof(float);                             \
+        if (dk == R * NR) {                                                                                                \
+            auto kern = delta_scan_staged_kernel<NR, R, TT, true>;                                                         \
             if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
             kern<<<grid, 128, smem, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);           \
         } else {                                                                                                           \
-            delta_scan_kernel<NR><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o); \
+            auto kern = delta_scan_staged_kernel<NR, R, TT, false>;                                                        \
+            if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            kern<<<grid, 128, smem, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);           \
         }                                                                                                                  \
     } while (0)
-    if (dk <= 32) B2_SCAN(8, 16);
-    else if (dk <= 64) B2_SCAN(16, 16);
-    else if (dk <= 128) B2_SCAN(32, 16);
-    else B2_SCAN(64, 8);
+    // chunks of several tokens: the per-token chain dominates, eight lanes a column; single tokens: the state streams
+    // through once, four lanes a column keep whole sectors
+    if (total_rows > 2 * n_seq) {
+        if (dk <= 32) B2_SCAN(4, 8, 16);
+        else if (dk <= 64) B2_SCAN(8, 8, 16);
+        else if (dk <= 128) B2_SCAN(16, 8, 16);
+        else B2_SCAN(32, 8, 8);
+    } else {
+        if (dk <= 32) B2_SCAN(8, 4, 16);
+        else if (dk <= 64) B2_SCAN(16, 4, 16);
+        else if (dk <= 128) B2_SCAN(32, 4, 16);
+        else B2_SCAN(64, 4, 8);
+    }
 #undef B2_SCAN
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;

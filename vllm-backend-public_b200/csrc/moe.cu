@@ -25,7 +25,7 @@ constexpr int kMoeBM = 32, kMoeBN = 64, kMoeBK = 32;
 // with four independent partial sums per lane), then warp 0 picks the `top` largest.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_r,
-                                 const float* __restrict__ bias, int D, int E, int top,
+                                 const float* __restrict__ bias, int D, int E, int top, bool vec,
                                  int32_t* __restrict__ ids, float* __restrict__ wts) {
     extern __shared__ float route_sm[];              // h [D] | z [E]
     float* hs = route_sm;
@@ -38,7 +38,21 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, cons
     for (int e = wid; e < E; e += nw) {
         const T* w = w_r + (size_t)e * D;
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        int i = lane;
+        if (vec) {                                   // 16 bytes of the weight row per lane and step
+            constexpr int VE = 16 / sizeof(T);
+            for (int i = lane * VE; i < D; i += 32 * VE) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+                const T* wv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int c = 0; c < VE; c += 4) {
+                    a0 = fmaf(hs[i + c], b2::ld(wv + c), a0);
+                    a1 = fmaf(hs[i + c + 1], b2::ld(wv + c + 1), a1);
+                    a2 = fmaf(hs[i + c + 2], b2::ld(wv + c + 2), a2);
+                    a3 = fmaf(hs[i + c + 3], b2::ld(wv + c + 3), a3);
+                }
+            }
+        }
+        int i = vec ? D : lane;
         for (; i + 96 < D; i += 128) {
             a0 = fmaf(hs[i], b2::ld(w + i), a0);
             a1 = fmaf(hs[i + 32], b2::ld(w + i + 32), a1);
@@ -155,11 +169,35 @@ __device__ __forceinline__ void load_tile(T* dst, F rowptr, int k0, int K, bool 
     }
 }
 
-// C[BM, BN] (+)= A[BM, K] B[BN, K]^T for NB B operands that share A (NB = 2: gate and up).  Result in c_sm[NB][BM][BN].
+__device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;                // 0: the 16 destination bytes are zero-filled, src is not read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(b2::smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+constexpr int kMoeStages = 3;
+
+// shared memory of one CTA: the operand stages, re-used for the fp32 result tile [NB][BM][BN] after the last k-step
+template <typename T, int NB>
+struct TileSmem {
+    static constexpr int LD = kMoeBK + Pad<T>::v;
+    static constexpr int A_EL = kMoeBM * LD, B_EL = NB * kMoeBN * LD, STAGE_EL = A_EL + B_EL;
+    static constexpr int STAGES = std::is_same<T, float>::value ? 1 : kMoeStages;
+    static constexpr int OPERAND_BYTES = STAGES * STAGE_EL * (int)sizeof(T);
+    static constexpr int C_BYTES = NB * kMoeBM * kMoeBN * (int)sizeof(float);
+    static constexpr int BYTES = OPERAND_BYTES > C_BYTES ? OPERAND_BYTES : C_BYTES;
+};
+
+// C[BM, BN] = A[BM, K] B[BN, K]^T for NB B operands that share A (NB = 2: gate and up).  Result as fp32 [NB][BM][BN] at
+// the start of `sm`.  bf16 with 16-byte aligned rows: a three-stage cp.async pipeline feeds 16x16x16 tensor-core
+// fragments, so the expert weights keep streaming while a k-step is multiplied (a decode batch is bound by that stream).
 template <typename T, int NB, typename FA, typename FB0, typename FB1>
-__device__ __forceinline__ void tile_product(FA a_row, FB0 b0_row, FB1 b1_row, int K, bool vec, T* a_sm, T* b_sm, float* c_sm) {
-    constexpr int LD = kMoeBK + Pad<T>::v;
+__device__ __forceinline__ void tile_product(FA a_row, FB0 b0_row, FB1 b1_row, int K, bool vec, unsigned char* sm) {
+    using L = TileSmem<T, NB>;
+    constexpr int LD = L::LD;
     const int tid = threadIdx.x;
+    T* a_sm = reinterpret_cast<T*>(sm);
+    T* b_sm = a_sm + L::A_EL;
+    float* c_sm = reinterpret_cast<float*>(sm);
     if constexpr (std::is_same<T, float>::value) {
         const int ty = tid >> 4, tx = tid & 15;      // rows ty*4 .. +3, columns tx + 16 c
         float acc[NB][4][4];
@@ -190,6 +228,7 @@ __device__ __forceinline__ void tile_product(FA a_row, FB0 b0_row, FB1 b1_row, i
                     }
             }
         }
+        __syncthreads();                             // every thread is done with the operands: the result takes their place
 #pragma unroll
         for (int b = 0; b < NB; ++b)
 #pragma unroll
@@ -205,26 +244,66 @@ __device__ __forceinline__ void tile_product(FA a_row, FB0 b0_row, FB1 b1_row, i
         for (int b = 0; b < NB; ++b)
 #pragma unroll
             for (int c = 0; c < 2; ++c) wmma::fill_fragment(acc[b][c], 0.f);
-        for (int k0 = 0; k0 < K; k0 += kMoeBK) {
-            __syncthreads();
-            load_tile<T, kMoeBM>(a_sm, a_row, k0, K, vec);
-            load_tile<T, kMoeBN>(b_sm, b0_row, k0, K, vec);
-            if (NB == 2) load_tile<T, kMoeBN>(b_sm + kMoeBN * LD, b1_row, k0, K, vec);
-            __syncthreads();
+        auto multiply = [&](const T* as, const T* bs) {
 #pragma unroll
             for (int kk = 0; kk < kMoeBK; kk += 16) {
                 wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
-                wmma::load_matrix_sync(fa, a_sm + (wm * 16) * LD + kk, LD);
+                wmma::load_matrix_sync(fa, as + (wm * 16) * LD + kk, LD);
 #pragma unroll
                 for (int b = 0; b < NB; ++b)
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
-                        wmma::load_matrix_sync(fb, b_sm + (b * kMoeBN + wn * 32 + c * 16) * LD + kk, LD);
+                        wmma::load_matrix_sync(fb, bs + (b * kMoeBN + wn * 32 + c * 16) * LD + kk, LD);
                         wmma::mma_sync(acc[b][c], fa, fb, acc[b][c]);
                     }
             }
+        };
+        if (vec) {
+            const T* safe = b0_row(0);               // a valid address for the copies that only zero-fill
+            auto issue = [&](int ks, int buf) {
+                T* as = a_sm + buf * L::STAGE_EL;
+                T* bs = as + L::A_EL;
+                const int k0 = ks * kMoeBK;
+                for (int idx = tid; idx < kMoeBM * (kMoeBK / 8); idx += 128) {
+                    const int r = idx / (kMoeBK / 8), kv = (idx % (kMoeBK / 8)) * 8;
+                    const T* p = a_row(r);
+                    const bool ok = p && k0 + kv < K;
+                    cp_async16_zfill(as + r * LD + kv, ok ? p + k0 + kv : safe, ok);
+                }
+                for (int idx = tid; idx < NB * kMoeBN * (kMoeBK / 8); idx += 128) {
+                    const int r = idx / (kMoeBK / 8), kv = (idx % (kMoeBK / 8)) * 8;
+                    const T* p = r < kMoeBN ? b0_row(r) : b1_row(r - kMoeBN);
+                    const bool ok = p && k0 + kv < K;
+                    cp_async16_zfill(bs + r * LD + kv, ok ? p + k0 + kv : safe, ok);
+                }
+            };
+            const int nk = (K + kMoeBK - 1) / kMoeBK;
+            for (int st = 0; st < kMoeStages - 1; ++st) {
+                if (st < nk) issue(st, st);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            for (int ks = 0; ks < nk; ++ks) {
+                asm volatile("cp.async.wait_group %0;" ::"n"(kMoeStages - 2) : "memory");
+                __syncthreads();                     // k-step ks has landed; the stage of k-step ks-1 is free again
+                const int nx = ks + kMoeStages - 1;
+                if (nx < nk) issue(nx, nx % kMoeStages);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                const T* as = a_sm + (ks % kMoeStages) * L::STAGE_EL;
+                multiply(as, as + L::A_EL);
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        } else {
+            for (int k0 = 0; k0 < K; k0 += kMoeBK) {
+                __syncthreads();
+                load_tile<T, kMoeBM>(a_sm, a_row, k0, K, false);
+                load_tile<T, kMoeBN>(b_sm, b0_row, k0, K, false);
+                if (NB == 2) load_tile<T, kMoeBN>(b_sm + kMoeBN * LD, b1_row, k0, K, false);
+                __syncthreads();
+                multiply(a_sm, b_sm);
+            }
         }
+        __syncthreads();                             // every warp is done with the operands: the result takes their place
 #pragma unroll
         for (int b = 0; b < NB; ++b)
 #pragma unroll
@@ -240,10 +319,8 @@ __global__ void __launch_bounds__(128)
 moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_gate, const T* __restrict__ w_up,
                    int64_t w13_expert_stride, const int32_t* __restrict__ sorted, const int32_t* __restrict__ tile_expert,
                    int top, int D, int F, bool vec, T* __restrict__ act) {
-    constexpr int LD = kMoeBK + Pad<T>::v;
-    __shared__ __align__(32) T a_sm[kMoeBM * LD];
-    __shared__ __align__(32) T b_sm[2 * kMoeBN * LD];
-    __shared__ __align__(32) float c_sm[2 * kMoeBM * kMoeBN];
+    __shared__ __align__(128) unsigned char sm[TileSmem<T, 2>::BYTES];
+    const float* c_sm = reinterpret_cast<const float*>(sm);
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
     const int m0 = blockIdx.x * kMoeBM, n0 = blockIdx.y * kMoeBN;
@@ -255,7 +332,7 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restric
     };
     auto g_row = [&](int r) -> const T* { return n0 + r < F ? wg + (size_t)(n0 + r) * D : nullptr; };
     auto u_row = [&](int r) -> const T* { return n0 + r < F ? wu + (size_t)(n0 + r) * D : nullptr; };
-    tile_product<T, 2>(a_row, g_row, u_row, D, vec, a_sm, b_sm, c_sm);
+    tile_product<T, 2>(a_row, g_row, u_row, D, vec, sm);
     for (int idx = threadIdx.x; idx < kMoeBM * kMoeBN; idx += blockDim.x) {
         const int r = idx / kMoeBN, c = idx % kMoeBN;
         if (n0 + c < F && sorted[m0 + r] >= 0) {
@@ -269,17 +346,15 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int32_t* __restrict__ sorted,
                 const int32_t* __restrict__ tile_expert, int D, int F, bool vec, float* __restrict__ rows) {
-    constexpr int LD = kMoeBK + Pad<T>::v;
-    __shared__ __align__(32) T a_sm[kMoeBM * LD];
-    __shared__ __align__(32) T b_sm[kMoeBN * LD];
-    __shared__ __align__(32) float c_sm[kMoeBM * kMoeBN];
+    __shared__ __align__(128) unsigned char sm[TileSmem<T, 1>::BYTES];
+    const float* c_sm = reinterpret_cast<const float*>(sm);
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
     const int m0 = blockIdx.x * kMoeBM, n0 = blockIdx.y * kMoeBN;
     const T* wd = w_down + (size_t)e * D * F;
     auto a_row = [&](int r) -> const T* { return sorted[m0 + r] >= 0 ? act + (size_t)(m0 + r) * F : nullptr; };
     auto d_row = [&](int r) -> const T* { return n0 + r < D ? wd + (size_t)(n0 + r) * F : nullptr; };
-    tile_product<T, 1>(a_row, d_row, d_row, F, vec, a_sm, b_sm, c_sm);
+    tile_product<T, 1>(a_row, d_row, d_row, F, vec, sm);
     for (int idx = threadIdx.x; idx < kMoeBM * kMoeBN; idx += blockDim.x) {
         const int r = idx / kMoeBN, c = idx % kMoeBN;
         if (n0 + c < D && sorted[m0 + r] >= 0) rows[(size_t)(m0 + r) * D + n0 + c] = c_sm[idx];
@@ -338,8 +413,9 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
     B2_DISPATCH_ACT(act_dtype, A, {
         auto kern = moe_route_kernel<A>;
         if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<T, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, D, E, top, ids,
-                                          weights);
+        const bool vec = D % (16 / (int)sizeof(A)) == 0 && b2_aligned16(w_router);
+        kern<<<T, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, D, E, top, vec,
+                                          ids, weights);
     });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
