@@ -141,13 +141,18 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
 // through warp 0's initial state.  Up to kGroupMaxHeads query heads per pass (more: further passes over the keys).
 constexpr int kGroupMaxHeads = 8, kGroupMaxPairs = 4;      // dv <= 256
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b2::smem_u32(dst)), "l"(src) : "memory");
+}
+
 __global__ void __launch_bounds__(128)
 chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                              const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_tables, int max_nb,
                              const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start, int n_seq, int H, int G,
                              int dk, int dv, int bs, float scale, int chunk, float sink, float sink_logit, int skip_rows_from,
                              __nv_bfloat16* __restrict__ out) {
-    extern __shared__ __align__(16) float grp_sm[];        // q [QH][dk] | per warp: m [QH], l [QH], acc [QH][dv]
+    // q [QH][dk] | per warp: m [QH], l [QH], acc [QH][dv] | per warp: K tile [32][dk + 8], V tile [32][dv] (bf16)
+    extern __shared__ __align__(16) float grp_sm[];
     const int row = blockIdx.x, g = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int seq = b2::seq_of_row(cu_q, n_seq, row);
@@ -166,6 +171,9 @@ chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
         const int QH = min(kGroupMaxHeads, QHall - h0);
         float* qs = grp_sm;
         float* part = grp_sm + kGroupMaxHeads * dk;
+        const int ldk = dk + 8;                            // 16 bytes of padding: the lanes' rows spread over the banks
+        __nv_bfloat16* kt = reinterpret_cast<__nv_bfloat16*>(part + 4 * kGroupMaxHeads * (2 + dv)) + (size_t)w * 32 * (ldk + dv);
+        __nv_bfloat16* vt = kt + 32 * ldk;
         __syncthreads();                                   // a previous pass is done with the shared memory
         for (int i = tid; i < QH * dk; i += 128)
             qs[i] = __bfloat162float(q[((size_t)row * H + (size_t)g * QHall + h0) * dk + i]) * scale;
@@ -184,11 +192,22 @@ chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
             float sc[kGroupMaxHeads];
 #pragma unroll
             for (int h = 0; h < kGroupMaxHeads; ++h) sc[h] = 0.f;
-            size_t vbase = 0;
+            // the warp's 32 keys: K and V rows gathered from the pages with every 16-byte copy in flight at once
+            const int nk = min(32, pos - j0 + 1);
+            __syncwarp();                                  // the previous tile has been read
+            for (int idx = lane; idx < nk * (dk / 8); idx += 32) {
+                const int key = idx / (dk / 8), c = (idx % (dk / 8)) * 8, jk = j0 + key;
+                cp_async16(kt + key * ldk + c, k_cache + (((size_t)bt[jk / bs] * G + g) * bs + jk % bs) * dk + c);
+            }
+            for (int idx = lane; idx < nk * (dv / 8); idx += 32) {
+                const int key = idx / (dv / 8), c = (idx % (dv / 8)) * 8, jk = j0 + key;
+                cp_async16(vt + key * dv + c, v_cache + (((size_t)bt[jk / bs] * G + g) * bs + jk % bs) * dv + c);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
             if (valid) {
-                const size_t tile = ((size_t)bt[j / bs] * G + g) * bs + (j % bs);
-                const __nv_bfloat16* kr = k_cache + tile * dk;
-                vbase = tile * dv;
+                const __nv_bfloat16* kr = kt + lane * ldk;
                 for (int c = 0; c < dk; c += 8) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
                     const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -229,16 +248,14 @@ chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                     }
                 }
             }
-            const int nk = min(32, pos - j0 + 1);
             for (int kk = 0; kk < nk; ++kk) {
-                const size_t vb = __shfl_sync(0xffffffffu, (unsigned long long)vbase, kk);
                 float vx[kGroupMaxPairs], vy[kGroupMaxPairs];
 #pragma unroll
                 for (int c = 0; c < kGroupMaxPairs; ++c) {
                     const int pi = lane + 32 * c;
                     vx[c] = vy[c] = 0.f;
                     if (pi < npairs) {
-                        const uint32_t wd = *reinterpret_cast<const uint32_t*>(v_cache + vb + 2 * pi);
+                        const uint32_t wd = *reinterpret_cast<const uint32_t*>(vt + kk * dv + 2 * pi);
                         vx[c] = __uint_as_float(wd << 16);
                         vy[c] = __uint_as_float(wd & 0xffff0000u);
                     }
@@ -524,10 +541,11 @@ extern "C" int b2_chunk_attention(void* out, const void* q, const void* k_cache,
 #undef B2_TILE
         if (rc != B2_OK) return rc;
     }
-    if (act_dtype == B2_ACT_BF16 && dk % 8 == 0 && dv % 2 == 0 && dv <= 64 * kGroupMaxPairs && b2_aligned16(q) &&
+    if (act_dtype == B2_ACT_BF16 && dk % 8 == 0 && dv % 8 == 0 && dv <= 64 * kGroupMaxPairs && b2_aligned16(q) &&
         b2_aligned16(k_cache) && b2_aligned16(v_cache) && b2_aligned16(out)) {
-        const size_t gsm = (size_t)(kGroupMaxHeads * dk + 4 * kGroupMaxHeads * (2 + dv)) * sizeof(float);
-        if (gsm <= 96 * 1024) {
+        const size_t gsm = (size_t)(kGroupMaxHeads * dk + 4 * kGroupMaxHeads * (2 + dv)) * sizeof(float) +
+                           (size_t)4 * 32 * (dk + 8 + dv) * sizeof(__nv_bfloat16);
+        if (gsm <= 160 * 1024) {
             auto kern = chunk_attention_group_kernel;
             if (gsm > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm));
             kern<<<dim3(T, G), 128, gsm, st>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
