@@ -34,7 +34,7 @@ def _batch(cuda, lens, ctx, slots, tables=None):
 
 
 # ------------------------------------------------------------------------------------------------ streams + norm
-@pytest.mark.parametrize("S,D", [(1, 48), (2, 200), (3, 64), (5, 33)])
+@pytest.mark.parametrize("S,D", [(1, 48), (2, 200), (3, 64), (5, 33), (9, 40)])
 @pytest.mark.parametrize("kind", ["layer", "rms"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_hc_step(cuda, S, D, kind, dtype):
@@ -262,7 +262,7 @@ def test_sink_and_padding_rows(cuda):
 
 # ------------------------------------------------------------------------------------------------ experts
 @pytest.mark.parametrize("T,D,F,E,top", [(1, 48, 20, 5, 2), (7, 64, 96, 3, 3), (70, 50, 18, 4, 1), (150, 40, 72, 12, 3),
-                                         (33, 256, 64, 40, 4)])
+                                         (33, 256, 64, 40, 4), (1100, 64, 16, 10, 3), (1027, 36, 8, 3, 2)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_router_and_experts(cuda, T, D, F, E, top, dtype):
     ops = _ops()

@@ -15,7 +15,7 @@
 
 namespace {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 
 template <typename T>
 __global__ void embed_streams_kernel(const T* __restrict__ embed, const int64_t* __restrict__ tokens, int D, int S,
@@ -153,7 +153,8 @@ extern "C" int b2_hc_step(float* x, int T, int S, int D, const void* y, int64_t 
         if (S == 1) B2_HC(1);
         else if (S == 2) B2_HC(2);
         else if (S <= 4) B2_HC(4);
-        else B2_HC(8);
+        else if (S <= 8) B2_HC(8);
+        else B2_HC(16);
     });
 #undef B2_HC
     B2_CUDA_OK(cudaGetLastError());

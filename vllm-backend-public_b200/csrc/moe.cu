@@ -21,75 +21,102 @@ namespace {
 constexpr int kMoeBM = 32, kMoeBN = 64, kMoeBK = 32;
 
 // ------------------------------------------------------------------------------------------------- router
-// One CTA per token: the row is staged once as fp32, the warps share the experts (each logit is one warp's dot product
-// with four independent partial sums per lane), then warp 0 picks the `top` largest.
-template <typename T>
+// One CTA per TOK tokens: their rows are staged once as fp32, the warps share the experts (each logit is one warp's dot
+// product with independent partial sums per lane; a weight vector is loaded once and applied to all TOK rows, which
+// divides the L2 traffic of a prompt batch by TOK), then warp t picks the `top` largest of token t.
+template <typename T, int TOK>
 __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_r,
-                                 const float* __restrict__ bias, int D, int E, int top, bool vec,
+                                 const float* __restrict__ bias, int rows, int D, int E, int top, bool vec, bool vec16,
                                  int32_t* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ float route_sm[];              // h [D] | z [E]
+    extern __shared__ float route_sm[];              // h [TOK][D] | z [TOK][E]
     float* hs = route_sm;
-    float* z = route_sm + D;
+    float* zs = route_sm + (size_t)TOK * D;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int t = blockIdx.x;
-    const T* x = h + (size_t)t * h_stride;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) hs[i] = b2::ld(x + i);
+    const int t0 = blockIdx.x * TOK;
+    const int nt = min(TOK, rows - t0);
+    for (int i = threadIdx.x; i < TOK * D; i += blockDim.x) {
+        const int tt = i / D;
+        hs[i] = tt < nt ? b2::ld(h + (size_t)(t0 + tt) * h_stride + (i - tt * D)) : 0.f;
+    }
     __syncthreads();
     for (int e = wid; e < E; e += nw) {
         const T* w = w_r + (size_t)e * D;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        if (vec) {                                   // 16 bytes of the weight row per lane and step
+        float a[TOK][2];
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) a[tt][0] = a[tt][1] = 0.f;
+        if (TOK == 1 && vec16) {                     // one token: 16 bytes of the weight row per lane and step
             constexpr int VE = 16 / sizeof(T);
             for (int i = lane * VE; i < D; i += 32 * VE) {
                 const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
                 const T* wv = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-                for (int c = 0; c < VE; c += 4) {
-                    a0 = fmaf(hs[i + c], b2::ld(wv + c), a0);
-                    a1 = fmaf(hs[i + c + 1], b2::ld(wv + c + 1), a1);
-                    a2 = fmaf(hs[i + c + 2], b2::ld(wv + c + 2), a2);
-                    a3 = fmaf(hs[i + c + 3], b2::ld(wv + c + 3), a3);
+                for (int c = 0; c < VE; c += 2) {
+                    a[0][0] = fmaf(hs[i + c], b2::ld(wv + c), a[0][0]);
+                    a[0][1] = fmaf(hs[i + c + 1], b2::ld(wv + c + 1), a[0][1]);
                 }
             }
+        } else if (vec) {                            // two weights per lane and step: the warp reads consecutive pairs,
+            for (int i = lane * 2; i < D; i += 64) { // and the TOK rows in shared memory without bank conflicts
+                float w0, w1;
+                if constexpr (std::is_same<T, float>::value) {
+                    const float2 wv = *reinterpret_cast<const float2*>(w + i);
+                    w0 = wv.x;
+                    w1 = wv.y;
+                } else {
+                    const uint32_t wv = *reinterpret_cast<const uint32_t*>(w + i);
+                    w0 = __uint_as_float(wv << 16);
+                    w1 = __uint_as_float(wv & 0xffff0000u);
+                }
+#pragma unroll
+                for (int tt = 0; tt < TOK; ++tt) {
+                    const float2 hv = *reinterpret_cast<const float2*>(hs + tt * D + i);
+                    a[tt][0] = fmaf(hv.x, w0, a[tt][0]);
+                    a[tt][1] = fmaf(hv.y, w1, a[tt][1]);
+                }
+            }
+        } else {
+            for (int i = lane; i < D; i += 32) {
+                const float w0 = b2::ld(w + i);
+#pragma unroll
+                for (int tt = 0; tt < TOK; ++tt) a[tt][0] = fmaf(hs[tt * D + i], w0, a[tt][0]);
+            }
         }
-        int i = vec ? D : lane;
-        for (; i + 96 < D; i += 128) {
-            a0 = fmaf(hs[i], b2::ld(w + i), a0);
-            a1 = fmaf(hs[i + 32], b2::ld(w + i + 32), a1);
-            a2 = fmaf(hs[i + 64], b2::ld(w + i + 64), a2);
-            a3 = fmaf(hs[i + 96], b2::ld(w + i + 96), a3);
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) {
+            const float v = b2::warp_sum(a[tt][0] + a[tt][1]);
+            if (lane == 0) zs[tt * E + e] = v + (bias ? bias[e] : 0.f);
         }
-        for (; i < D; i += 32) a0 = fmaf(hs[i], b2::ld(w + i), a0);
-        const float a = b2::warp_sum((a0 + a1) + (a2 + a3));
-        if (lane == 0) z[e] = a + (bias ? bias[e] : 0.f);
     }
     __syncthreads();
-    if (wid != 0) return;
-    float v0 = 0.f, sum = 0.f;
-    for (int j = 0; j < top; ++j) {
-        float best = -INFINITY;
-        int arg = 0x7fffffff;
-        for (int e = lane; e < E; e += 32)
-            if (z[e] > best) { best = z[e]; arg = e; }
+    for (int tt = wid; tt < nt; tt += nw) {
+        float* z = zs + (size_t)tt * E;
+        const int t = t0 + tt;
+        float v0 = 0.f, sum = 0.f;
+        for (int j = 0; j < top; ++j) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int e = lane; e < E; e += 32)
+                if (z[e] > best) { best = z[e]; arg = e; }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (arg == 0x7fffffff) arg = 0;          // every logit is NaN or -inf: still a valid expert id
+            if (j == 0) v0 = best;
+            const float p = expf(best - v0);
+            sum += p;
+            if (lane == 0) {
+                ids[(size_t)t * top + j] = arg;
+                wts[(size_t)t * top + j] = p;
+                z[arg] = -INFINITY;
+            }
+            __syncwarp();
         }
-        if (arg == 0x7fffffff) arg = 0;              // every logit is NaN or -inf: still a valid expert id
-        if (j == 0) v0 = best;
-        const float p = expf(best - v0);
-        sum += p;
-        if (lane == 0) {
-            ids[(size_t)t * top + j] = arg;
-            wts[(size_t)t * top + j] = p;
-            z[arg] = -INFINITY;
-        }
-        __syncwarp();
+        const float inv = 1.f / sum;
+        for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= inv;
     }
-    const float inv = 1.f / sum;
-    for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= inv;
 }
 
 // ------------------------------------------------------------------------------------------------- align
@@ -406,16 +433,26 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
     B2_REQUIRE(T >= 0 && D > 0 && E > 0 && top >= 1 && top <= E, B2_EINVAL, "moe_route: bad sizes D=%d E=%d top=%d", D, E, top);
     if (T == 0) return B2_OK;
     B2_REQUIRE(h && w_router && ids && weights, B2_EINVAL, "moe_route: null pointer");
-    const size_t smem = (size_t)(D + E) * sizeof(float);
+    // prompt batches: four tokens share a CTA (and every weight load); small batches keep a CTA per token
+    const int tok = (T >= 1024 && (size_t)4 * (D + E) * sizeof(float) <= 96 * 1024) ? 4 : 1;
+    const size_t smem = (size_t)tok * (D + E) * sizeof(float);
     B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "moe_route: width %d and %d experts do not fit shared memory", D, E);
-    const int warps = E < 8 ? (E < 2 ? 2 : E) : 8;
+    const int warps = E < 8 ? (E < 4 ? 4 : E) : 8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     B2_DISPATCH_ACT(act_dtype, A, {
-        auto kern = moe_route_kernel<A>;
-        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        const bool vec = D % (16 / (int)sizeof(A)) == 0 && b2_aligned16(w_router);
-        kern<<<T, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, D, E, top, vec,
-                                          ids, weights);
+        const bool vec = D % 2 == 0 && b2_aligned16(w_router);
+        const bool vec16 = D % (16 / (int)sizeof(A)) == 0 && b2_aligned16(w_router);
+        if (tok == 4) {
+            auto kern = moe_route_kernel<A, 4>;
+            if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<(T + 3) / 4, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias,
+                                                        T, D, E, top, vec, vec16, ids, weights);
+        } else {
+            auto kern = moe_route_kernel<A, 1>;
+            if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<T, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, T, D, E, top,
+                                              vec, vec16, ids, weights);
+        }
     });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
