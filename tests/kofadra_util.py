@@ -55,6 +55,11 @@ def cfg_d():      # four streams, the whole stack looped three times, long convo
                   loop=(0, 2, 3))
 
 
+def cfg_e():      # head sizes the tensor-core prompt kernel takes in bf16 (multiples of 32), dk != dv, three streams
+    return config(96, 200, [attn(4, 2, 32, 64, chunk=24, scale=0.25, mlp=moe(8, 2, 32)), delta(2, 2, 32, 32, 4, moe(8, 3, 24)),
+                            attn(2, 1, 64, 32, chunk=40)], streams=3, loop=(0, 1, 2))
+
+
 def save_checkpoint(path: Path, cfg: dict, weights: Dict[str, torch.Tensor]) -> Path:
     from safetensors.torch import save_file
     path.mkdir(parents=True, exist_ok=True)

@@ -10,7 +10,7 @@ import kofadra_util as U
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"a": U.cfg_a, "b": U.cfg_b, "c": U.cfg_c, "d": U.cfg_d}
+CONFIGS = {"a": U.cfg_a, "b": U.cfg_b, "c": U.cfg_c, "d": U.cfg_d, "e": U.cfg_e}
 
 
 @pytest.fixture(scope="module")
@@ -56,7 +56,8 @@ def test_portions_of_many_sizes(cuda, models, name):
     eng.close()
 
 
-@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("d", "float32"), ("a", "bfloat16"), ("c", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("d", "float32"), ("e", "float32"),
+                                        ("a", "bfloat16"), ("c", "bfloat16"), ("e", "bfloat16")])
 def test_unequal_batches_with_reuse_of_pages_and_slots(cuda, models, name, dtype):
     """Up to four live requests, prompt portions beside single tokens; requests leave and new ones take over their pages
     and state slots (a pool of 16 pages for ~320 tokens in total).  Every request equals the oracle over its own tokens,
@@ -144,3 +145,57 @@ def test_random_init_and_checkpoint_shape_check(cuda, tmp_path, models):
     U.save_checkpoint(tmp_path / "bad", cfg, bad)
     with pytest.raises(ValueError, match="A_log"):
         U.make_engine(tmp_path / "bad", "bfloat16")
+
+
+def test_server_serves_a_model_directory(cuda, models):
+    """`python -m b200attn.server --model DIR --dtype float32`: the family comes from config.json, completions are the
+    oracle's greedy continuation of a token-id prompt."""
+    import os
+    import subprocess
+    import sys
+    import time
+    from pathlib import Path
+
+    import requests
+    import socket
+    cfg, W, path = models["b"]
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root / "vllm-backend-public_b200"))
+    proc = subprocess.Popen([sys.executable, "-m", "b200attn.server", "--model", str(path), "--dtype", "float32", "--port", str(port),
+                             "--host", "127.0.0.1", "--max-num-seqs", "4", "--max-model-len", "256",
+                             "--num-gpu-blocks-override", "80", "--served-model-name", "kofadra-test"], env=env,
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        for _ in range(600):
+            if proc.poll() is not None:
+                raise RuntimeError("server exited: " + proc.stdout.read().decode()[-2000:])
+            try:
+                if requests.get(base + "/health", timeout=1).status_code == 200:
+                    break
+            except requests.RequestException:
+                pass
+            time.sleep(0.2)
+        else:
+            raise RuntimeError("server did not become healthy")
+        prompt = U.tokens(11, cfg["vocab"], 77)
+        r = requests.post(base + "/v1/completions", json={"model": "kofadra-test", "prompt": prompt, "max_tokens": 6,
+                                                          "temperature": 0.0, "ignore_eos": True}, timeout=60)
+        assert r.status_code == 200, r.text
+        body = r.json()
+        assert body["usage"]["prompt_tokens"] == 11 and body["usage"]["completion_tokens"] == 6
+        seq = list(prompt)
+        for _ in range(6):
+            seq.append(int(U.oracle_logits(cfg, W, seq)[-1].argmax()))
+        want = bytes(t % 256 for t in seq[11:]).decode("utf-8", errors="replace")      # the byte tokenizer's text
+        assert body["choices"][0]["text"] == want
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(20)
+        except subprocess.TimeoutExpired:
+            proc.kill()

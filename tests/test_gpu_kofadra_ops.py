@@ -200,7 +200,9 @@ def _attn_oracle(qkv, q_w, k_w, H, G, dk, dv, eps, scale, chunk):
                                                 (2, 1, 8, 24, 16, 0), (5, 5, 40, 8, 32, 5),
                                                 # head sizes the tensor-core prompt kernel takes (bf16, portions of >= 16 rows)
                                                 (4, 2, 64, 32, 16, 24), (2, 1, 128, 128, 16, 100), (2, 2, 32, 96, 8, 0),
-                                                (4, 4, 96, 96, 16, 64), (2, 1, 64, 64, 16, 7)])
+                                                (4, 4, 96, 96, 16, 64), (2, 1, 64, 64, 16, 7),
+                                                # more than eight query heads per kv head; sizes only the warp kernel takes
+                                                (12, 1, 16, 8, 16, 10), (2, 1, 12, 20, 16, 6)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_chunk_attention_in_portions_over_scattered_pages(cuda, H, G, dk, dv, bs, chunk, dtype):
     """Two sequences: prompt portions that end inside a page and inside a mask block, then single rows; queries and
