@@ -104,7 +104,7 @@ def _delta_oracle(proj, conv_w, A_log, dt_bias, norm_w, H, G, dk, dv, eps):
 
 
 @pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 16, 24, 3), (2, 2, 40, 72, 1), (3, 1, 8, 8, 6), (2, 1, 128, 64, 4),
-                                            (1, 1, 200, 40, 2)])
+                                            (1, 1, 200, 40, 2), (1, 1, 30, 6, 3), (1, 1, 300, 8, 2)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_delta_mixer_stages_with_state_across_calls(cuda, H, G, dk, dv, taps, dtype):
     """Two sequences of unequal length fed in portions (down to one and two tokens), their slots swapped relative to
@@ -202,7 +202,7 @@ def _attn_oracle(qkv, q_w, k_w, H, G, dk, dv, eps, scale, chunk):
                                                 (4, 2, 64, 32, 16, 24), (2, 1, 128, 128, 16, 100), (2, 2, 32, 96, 8, 0),
                                                 (4, 4, 96, 96, 16, 64), (2, 1, 64, 64, 16, 7),
                                                 # more than eight query heads per kv head; sizes only the warp kernel takes
-                                                (12, 1, 16, 8, 16, 10), (2, 1, 12, 20, 16, 6)])
+                                                (12, 1, 16, 8, 16, 10), (2, 1, 12, 20, 16, 6), (1, 1, 8, 320, 16, 9)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_chunk_attention_in_portions_over_scattered_pages(cuda, H, G, dk, dv, bs, chunk, dtype):
     """Two sequences: prompt portions that end inside a page and inside a mask block, then single rows; queries and

@@ -20,7 +20,7 @@
 
 namespace {
 
-constexpr int kMaxDvPerLane = 8;                     // dv <= 256
+constexpr int kMaxDvPerLane = 16;                    // dv <= 512
 
 template <typename T>
 __global__ void qknorm_cache_kernel(const T* __restrict__ qkv, int64_t qkv_stride, int H, int G, int dk, int dv,

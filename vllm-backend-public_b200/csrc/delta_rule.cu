@@ -384,17 +384,18 @@ extern "C" int b2_delta_scan(const float* qkv, const float* beta, const float* d
                              int dv, const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
                              float* state, float* o, void* stream) {
     B2_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, B2_EINVAL, "delta_scan: bad sizes");
-    B2_REQUIRE(dk <= 256, B2_EUNSUPPORTED, "delta_scan: key size %d above 256", dk);
+    B2_REQUIRE(dk <= 512, B2_EUNSUPPORTED, "delta_scan: key size %d above 512", dk);
     if (n_seq == 0) return B2_OK;
     B2_REQUIRE(qkv && beta && decay && cu_q && ctx_start && state_slot && state && o, B2_EINVAL, "delta_scan: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool staged = dk % 4 == 0 && dv % 4 == 0 && b2_aligned16(qkv);       // rows of 2*G*dk + H*dv floats stay aligned
+    const bool staged = dk % 4 == 0 && dv % 4 == 0 && dk <= 256 && b2_aligned16(qkv);       // rows of 2*G*dk + H*dv floats stay aligned
     if (!staged) {
         const dim3 grid(n_seq, H, (dv + 31) / 32);
         if (dk <= 32) delta_scan_kernel<8><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
         else if (dk <= 64) delta_scan_kernel<16><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
         else if (dk <= 128) delta_scan_kernel<32><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
-        else delta_scan_kernel<64><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
+        else if (dk <= 256) delta_scan_kernel<64><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
+        else delta_scan_kernel<128><<<grid, 128, 0, st>>>(qkv, beta, decay, H, G, dk, dv, cu_q, ctx_start, state_slot, state, o);
         B2_CUDA_OK(cudaGetLastError());
         return B2_OK;
     }
