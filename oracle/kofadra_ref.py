@@ -17,10 +17,6 @@ import torch
 F64 = torch.float64
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def silu(z):
     return z * torch.sigmoid(z)
 
