@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 2
+#define B2_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define B2_API __attribute__((visibility("default")))
@@ -465,7 +465,8 @@ B2_API int b2_comm_push_allreduce_rms_norm(void* comm, const void* partial, int6
 B2_API int b2_comm_allgather_cols(void* comm, const void* local, int64_t local_stride, int T, int cols, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Building blocks of decoders beyond the Llama layer (hyper_norm.cu, delta_rule.cu, chunk_attention.cu, moe.cu).
+ * Building blocks of decoders beyond the Llama layer (hyper_norm.cu, delta_rule.cu, chunk_attention.cu, moe.cu,
+ * post_norm.cu, latent_attention.cu).
  * Every op exists for two activation types: B2_ACT_BF16 (weights, activations and caches in bf16) and B2_ACT_F32
  * (everything in fp32).  The residual streams, all statistics, softmax, router logits and recurrent state are fp32 in
  * both.  Small parameter vectors (norm weights, convolution taps, gates' constants, router bias, stream mixing) are
@@ -501,8 +502,12 @@ B2_API int b2_chunk_attention(void* out, const void* q, const void* k_cache, con
                               float sink_logit, void* stream);
 B2_API int b2_moe_tile_rows(void);
 B2_API int b2_moe_capacity(int n, int E);
+#define B2_ROUTE_TOPK_SOFTMAX 0   /* top-k of logits + bias, weights = softmax over the chosen logits */
+#define B2_ROUTE_SOFTMAX_ALL  1   /* s = softmax over all experts, top-k of s + bias, weights = the chosen s as they are */
+#define B2_GLU_SILU    0          /* silu(g) * u */
+#define B2_GLU_CLAMPED 1          /* g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(alpha g') * (u' + 1) */
 B2_API int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
-                        int D, int E, int top, int32_t* ids, float* weights, void* stream);
+                        int D, int E, int top, int scoring, int32_t* ids, float* weights, void* stream);
 B2_API int b2_moe_align(const int32_t* ids, int n, int E, int cap, int32_t* sorted, int32_t* tile_expert, int32_t* place,
                         int32_t* group_ends /* [E] or NULL */, void* stream);
 B2_API int b2_moe_gather(const void* h, int64_t h_stride, int act_dtype, const int32_t* sorted, int cap, int top, int D,
@@ -513,7 +518,25 @@ B2_API int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gate, c
                           int64_t w13_expert_stride /* elements between experts of w_gate / w_up (>= F*D) */,
                           int act_dtype, int T, int D, int F, int top, int cap, const int32_t* sorted,
                           const int32_t* tile_expert, const int32_t* place, const float* weights, void* act, float* rows,
-                          void* y, int64_t y_stride, void* stream);
+                          void* y, int64_t y_stride, int glu, float glu_alpha, float glu_limit, void* stream);
+/* post_norm.cu: norms on both sides of a sublayer around an fp32 residual, element-wise activations, logit soft cap */
+B2_API int b2_sandwich_norm(float* x, int T, int D, const void* y, int64_t y_stride, const float* post_w,
+                            const float* post_b, const float* pre_w, const float* pre_b, float eps, int norm_kind, void* h,
+                            int64_t h_stride, int act_dtype, void* stream);
+B2_API int b2_relu_sq(void* out, int64_t out_stride, const void* in, int64_t in_stride, int act_dtype, int T, int I,
+                      void* stream);
+B2_API int b2_glu_and_mul(void* out, int64_t out_stride, const void* gate_up, int64_t in_stride, int act_dtype, int T, int I,
+                          int glu, float alpha, float limit, void* stream);
+B2_API int b2_softcap(void* z, int64_t stride, int act_dtype, int T, int V, float cap, void* stream);
+/* latent_attention.cu: attention over one shared low-rank latent + one shared rotated key part per token */
+B2_API int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dtype, int T, int H, int dn, int dr, int rot_dims,
+                          int R, int q_off, int dkv_off /* < 0: the layer reads another layer's pool */, const float* norm_w,
+                          float eps, const int32_t* positions, const float* cos_sin, int max_pos, const int64_t* slots, int bs,
+                          void* qa, void* cache, void* stream);
+B2_API int b2_latent_attention(void* out, const void* qa, const void* cache, int act_dtype, const int32_t* block_tables,
+                               int max_nb, const int32_t* cu_q, const int32_t* ctx_start, int n_seq, int T, int H, int R,
+                               int dr, int bs, float scale, int window /* 0: causal */, const void* gate /* or NULL */,
+                               int64_t gate_stride, void* stream);
 
 #ifdef __cplusplus
 }

@@ -354,15 +354,7 @@ class KofadraModel:
             raise ValueError("decode rows need their state slots")
         if npf and prefill.state_slots is None:
             raise ValueError("prompt chunks need their state slots")
-        if not npf:
-            return ops.SeqBatch(self._arange[:n_decode + 1], dec_sl - 1, dec_bt, dec_state, n_decode, n_decode)
-        rows = n_decode + prefill.total_tokens
-        if not n_decode:
-            return ops.SeqBatch(prefill.cu_q, prefill.ctx_start, prefill.block_tables, prefill.state_slots, npf, rows)
-        return ops.SeqBatch(torch.cat([self._arange[:n_decode], prefill.cu_q + n_decode]),
-                            torch.cat([dec_sl - 1, prefill.ctx_start]),
-                            torch.cat([dec_bt, prefill.block_tables]).contiguous(),
-                            torch.cat([dec_state, prefill.state_slots]), n_decode + npf, rows)
+        return ops.step_batch(self._arange, n_decode, dec_bt, dec_sl, dec_state, prefill)
 
     def _hc(self, li: int, q: int):
         """(in, out, mix) of sublayer q of layer li; None = the plain residual's ones / identity."""

@@ -405,8 +405,9 @@ class LlamaModel:
 
 
 def _register_families() -> None:
-    from . import kofadra
+    from . import gatolix, kofadra
     ARCHITECTURES[kofadra.ARCHITECTURE] = kofadra.config_from_dir
+    ARCHITECTURES[gatolix.ARCHITECTURE] = gatolix.config_from_dir
 
 
 _register_families()

@@ -642,7 +642,8 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, see
 # ======================================================================================================================
 from dataclasses import dataclass  # noqa: E402
 
-from ._lib import ACT_BF16, ACT_F32, NORM_LAYER, NORM_RMS  # noqa: E402,F401
+from ._lib import (ACT_BF16, ACT_F32, GLU_CLAMPED, GLU_SILU, NORM_LAYER, NORM_RMS,  # noqa: E402,F401
+                   ROUTE_SOFTMAX_ALL, ROUTE_TOPK_SOFTMAX)
 
 
 def _act(t: torch.Tensor, name: str) -> int:
@@ -678,6 +679,21 @@ class SeqBatch:
     state_slots: Optional[torch.Tensor]      # [n]; < 0: the sequence keeps no recurrent state
     n_seq: int
     rows: int
+
+
+def step_batch(arange: torch.Tensor, n_decode: int, dec_bt, dec_sl, dec_state, prefill) -> SeqBatch:
+    """[decode rows | prompt chunks] of one engine step as one list of sequences.  arange: int32 [>= n_decode + 1] =
+    0, 1, 2, ...; dec_sl: the decode rows' sequence lengths INCLUDING the new token (0 = padding row); prefill: the step's
+    PrefillBatch or None."""
+    npf = prefill.cu_q.shape[0] - 1 if prefill is not None and prefill.total_tokens else 0
+    if not npf:
+        return SeqBatch(arange[:n_decode + 1], dec_sl - 1, dec_bt, dec_state, n_decode, n_decode)
+    rows = n_decode + prefill.total_tokens
+    if not n_decode:
+        return SeqBatch(prefill.cu_q, prefill.ctx_start, prefill.block_tables, prefill.state_slots, npf, rows)
+    state = None if dec_state is None or prefill.state_slots is None else torch.cat([dec_state, prefill.state_slots])
+    return SeqBatch(torch.cat([arange[:n_decode], prefill.cu_q + n_decode]), torch.cat([dec_sl - 1, prefill.ctx_start]),
+                    torch.cat([dec_bt, prefill.block_tables]).contiguous(), state, n_decode + npf, rows)
 
 
 def embed_streams(embed: torch.Tensor, tokens: torch.Tensor, streams: int, scale: float) -> torch.Tensor:
@@ -828,8 +844,11 @@ def chunk_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return out
 
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int):
-    """ids int32 [T, top], weights fp32 [T, top]: the top logits of h W_r^T + bias (fp32), softmax over the chosen."""
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
+              scoring: int = ROUTE_TOPK_SOFTMAX):
+    """ids int32 [T, top], weights fp32 [T, top] from the fp32 logits z = h W_r^T.  ROUTE_TOPK_SOFTMAX: the top z + bias,
+    weights = softmax over the chosen; ROUTE_SOFTMAX_ALL: s = softmax(z) over all experts, the top s + bias are chosen,
+    weights = their s, not renormalised."""
     lib = _lib.load()
     dev = _need_cuda(h=h, w_router=w_router, bias=bias)
     T, D, hs = _mat(h, "h")
@@ -839,8 +858,8 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
     _f32(bias, "bias", (E,))
     ids = torch.empty(T, top, dtype=torch.int32, device=dev)
     wts = torch.empty(T, top, dtype=torch.float32, device=dev)
-    _lib.check(lib.b2_moe_route(_ptr(h), hs, _ptr(w_router), _ptr(bias), _act(h, "h"), T, D, E, top, _ptr(ids), _ptr(wts),
-                                _stream(dev)))
+    _lib.check(lib.b2_moe_route(_ptr(h), hs, _ptr(w_router), _ptr(bias), _act(h, "h"), T, D, E, top, int(scoring), _ptr(ids),
+                                _ptr(wts), _stream(dev)))
     return ids, wts
 
 
@@ -851,8 +870,10 @@ MOE_GROUPED_GEMM_MIN_PAIRS = 2048
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                w_down: torch.Tensor, w_gate_up: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y[t] = sum_j wts[t, j] * W_down[e] (silu(W_gate[e] h[t]) * (W_up[e] h[t])), e = ids[t, j].
+                w_down: torch.Tensor, w_gate_up: Optional[torch.Tensor] = None, glu: int = GLU_SILU,
+                glu_alpha: float = 1.0, glu_limit: float = 0.0) -> torch.Tensor:
+    """y[t] = sum_j wts[t, j] * W_down[e] glu(W_gate[e] h[t], W_up[e] h[t]), e = ids[t, j]; glu = silu(g) * u (GLU_SILU) or
+    the bounded unit min(g, limit) * sigmoid(alpha min(g, limit)) * (clamp(u, +-limit) + 1) (GLU_CLAMPED).
     w_gate, w_up [E, F, D]; w_down [E, D, F]; w_gate_up [E, 2F, D] (optional): the two stacked per expert -- w_gate and
     w_up may be views of it.  Sorting by expert (b2_moe_align), both products and the weighted sum (in fp32, choice order)
     run on the device without a host read: b2_moe_experts, or for large bf16 batches b2_moe_gather -> grouped GEMM ->
@@ -886,7 +907,7 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: t
         a = torch.empty(cap, D, dtype=h.dtype, device=dev)
         _lib.check(lib.b2_moe_gather(_ptr(h), hs, _act(h, "h"), _ptr(srt), cap, top, D, _ptr(a), _stream(dev)))
         gu = torch._grouped_mm(a, w_gate_up.transpose(1, 2), offs=ends)              # [cap, 2F]; rows past the last group unset
-        act = silu_and_mul(gu)
+        act = silu_and_mul(gu) if glu == GLU_SILU else glu_and_mul(gu, glu, glu_alpha, glu_limit)
         rows = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)             # [cap, D]
         _lib.check(lib.b2_moe_combine(_ptr(rows), 0, _ptr(place), _ptr(wts), T, top, D, _ptr(y), D, _act(h, "h"), _stream(dev)))
         return y
@@ -894,5 +915,155 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: t
     rows = torch.empty(cap, D, dtype=torch.float32, device=dev)
     _lib.check(lib.b2_moe_experts(_ptr(h), hs, _ptr(w_gate), _ptr(w_up), _ptr(w_down), w_gate.stride(0), _act(h, "h"), T, D, F,
                                   top, cap, _ptr(srt), _ptr(tile_e), _ptr(place), _ptr(wts), _ptr(act), _ptr(rows), _ptr(y), D,
-                                  _stream(dev)))
+                                  int(glu), float(glu_alpha), float(glu_limit), _stream(dev)))
     return y
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# csrc/post_norm.cu, csrc/latent_attention.cu
+# ----------------------------------------------------------------------------------------------------------------------
+def sandwich_norm(x: torch.Tensor, y: Optional[torch.Tensor] = None, post_w: Optional[torch.Tensor] = None,
+                  post_b: Optional[torch.Tensor] = None, pre_w: Optional[torch.Tensor] = None,
+                  pre_b: Optional[torch.Tensor] = None, eps: float = 1e-6, norm_kind: int = NORM_LAYER,
+                  h_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """One pass over the fp32 residual x [T, D] (updated in place): with y [T, D], x <- x + norm(y) * post_w + post_b
+    (post_w None: x <- x + y); with pre_w, returns h = norm(x) * pre_w + pre_b as h_dtype.  b2_sandwich_norm."""
+    lib = _lib.load()
+    dev = _need_cuda(x=x, y=y, post_w=post_w, post_b=post_b, pre_w=pre_w, pre_b=pre_b)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be contiguous fp32 [T, D]")
+    T, D = x.shape
+    ys = 0
+    if y is not None:
+        Ty, Dy, ys = _mat(y, "y")
+        if (Ty, Dy) != (T, D):
+            raise ValueError("y must be [T, D]")
+    for n, v in (("post_w", post_w), ("post_b", post_b), ("pre_w", pre_w), ("pre_b", pre_b)):
+        _f32(v, n, (D,))
+    if (post_b is not None and post_w is None) or (pre_b is not None and pre_w is None):
+        raise ValueError("a norm bias needs its weight")
+    h = None
+    if pre_w is not None:
+        h_dtype = h_dtype or (y.dtype if y is not None else torch.bfloat16)
+        h = torch.empty(T, D, dtype=h_dtype, device=dev)
+    if h is not None and y is not None and h.dtype != y.dtype:
+        raise ValueError("h_dtype must equal y's dtype")
+    act = _act(h if h is not None else y, "h / y") if (h is not None or y is not None) else ACT_BF16
+    _lib.check(lib.b2_sandwich_norm(_ptr(x), T, D, _ptr(y), ys, _ptr(post_w), _ptr(post_b), _ptr(pre_w), _ptr(pre_b),
+                                    float(eps), norm_kind, _ptr(h), D, act, _stream(dev)))
+    return h
+
+
+def relu_sq(x: torch.Tensor) -> torch.Tensor:
+    """max(x, 0)^2 over rows [T, I].  b2_relu_sq."""
+    lib = _lib.load()
+    dev = _need_cuda(x=x)
+    T, I, xs = _mat(x, "x")
+    out = torch.empty(T, I, dtype=x.dtype, device=dev)
+    _lib.check(lib.b2_relu_sq(_ptr(out), I, _ptr(x), xs, _act(x, "x"), T, I, _stream(dev)))
+    return out
+
+
+def glu_and_mul(gate_up: torch.Tensor, glu: int = GLU_SILU, alpha: float = 1.0, limit: float = 0.0) -> torch.Tensor:
+    """Rows [gate | up] of width 2I -> glu(gate, up) [T, I] (see moe_experts).  b2_glu_and_mul."""
+    lib = _lib.load()
+    dev = _need_cuda(gate_up=gate_up)
+    T, W, gs = _mat(gate_up, "gate_up")
+    if W % 2:
+        raise ValueError("gate_up must hold gate and up halves")
+    out = torch.empty(T, W // 2, dtype=gate_up.dtype, device=dev)
+    _lib.check(lib.b2_glu_and_mul(_ptr(out), W // 2, _ptr(gate_up), gs, _act(gate_up, "gate_up"), T, W // 2, int(glu),
+                                  float(alpha), float(limit), _stream(dev)))
+    return out
+
+
+def softcap_(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """z <- cap * tanh(z / cap) in place over rows [T, V].  b2_softcap."""
+    lib = _lib.load()
+    dev = _need_cuda(z=z)
+    T, V, zs = _mat(z, "z")
+    _lib.check(lib.b2_softcap(_ptr(z), zs, _act(z, "z"), T, V, float(cap), _stream(dev)))
+    return z
+
+
+def rotary_table(max_pos: int, dims: int, base: float, scaling: Optional[dict], device) -> torch.Tensor:
+    """fp32 [max_pos, dims] = cos | sin halves per position for the interleaved pairing (2i, 2i + 1), angles in fp64.
+    scaling {factor, original, fast, slow} (YaRN): pairs that complete more than `fast` turns within `original` positions
+    keep their frequency, pairs below `slow` turns are slowed by `factor`, a linear ramp over the pair index between the
+    two; cos and sin carry the magnitude 0.1 ln(factor) + 1."""
+    half = dims // 2
+    f = base ** (-2.0 * torch.arange(half, dtype=torch.float64) / dims)
+    mag = 1.0
+    if scaling:
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+
+        def turn_dim(t):
+            return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+
+        lo = max(math.floor(turn_dim(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(turn_dim(float(scaling["slow"]))), dims - 1)
+        ramp = ((torch.arange(half, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        f = f / factor * ramp + f * (1.0 - ramp)
+        mag = 0.1 * math.log(factor) + 1.0
+    ang = torch.arange(max_pos, dtype=torch.float64).unsqueeze(1) * f.unsqueeze(0)
+    return (torch.cat([torch.cos(ang), torch.sin(ang)], dim=1) * mag).to(torch.float32).contiguous().to(device)
+
+
+def latent_prep(proj: torch.Tensor, H: int, dn: int, dr: int, rot_dims: int, R: int, q_off: int, dkv_off: int,
+                norm_w: Optional[torch.Tensor], eps: float, positions: torch.Tensor, cos_sin: torch.Tensor,
+                slots: Optional[torch.Tensor], cache: Optional[torch.Tensor], qa: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows proj [T, ...] hold the query heads [dn | dr] from column q_off and, when dkv_off >= 0, the down-projection
+    [R | dr] from column dkv_off.  Writes the rotated dr part of every query head to qa[t, h, R:], and (dkv_off >= 0) the
+    RMS-normed latent and the rotated shared key part to cache [nb, bs, R + dr] at slots[t] (< 0 skips).  Returns qa
+    [T, H, R + dr] of proj's dtype, whose first R columns per head are left for the absorbed query.  b2_latent_prep."""
+    lib = _lib.load()
+    dev = _need_cuda(proj=proj, norm_w=norm_w, positions=positions, cos_sin=cos_sin, slots=slots, cache=cache, qa=qa)
+    T, P, ps = _mat(proj, "proj")
+    if q_off + H * (dn + dr) > P or (dkv_off >= 0 and dkv_off + R + dr > P):
+        raise ValueError("proj is narrower than its column map")
+    if positions.dtype != torch.int32 or positions.shape != (T,) or not positions.is_contiguous():
+        raise ValueError("positions must be contiguous int32 [T]")
+    if cos_sin.dtype != torch.float32 or cos_sin.dim() != 2 or cos_sin.shape[1] != rot_dims or not cos_sin.is_contiguous():
+        raise ValueError(f"cos_sin must be contiguous fp32 [max_pos, {rot_dims}]")
+    bs = 1
+    if dkv_off >= 0:
+        _f32(norm_w, "norm_w", (R,))
+        if cache is None or cache.dim() != 3 or cache.shape[2] != R + dr or not cache.is_contiguous() or cache.dtype != proj.dtype:
+            raise ValueError("cache must be contiguous [nb, bs, R + dr] of proj's dtype")
+        if slots is None or slots.dtype != torch.int64 or slots.shape != (T,) or not slots.is_contiguous():
+            raise ValueError("slots must be contiguous int64 [T]")
+        bs = cache.shape[1]
+    if qa is None:
+        qa = torch.empty(T, H, R + dr, dtype=proj.dtype, device=dev)
+    elif tuple(qa.shape) != (T, H, R + dr) or qa.dtype != proj.dtype or not qa.is_contiguous():
+        raise ValueError("qa must be contiguous [T, H, R + dr] of proj's dtype")
+    _lib.check(lib.b2_latent_prep(_ptr(proj), ps, _act(proj, "proj"), T, H, dn, dr, rot_dims, R, q_off, dkv_off, _ptr(norm_w),
+                                  float(eps), _ptr(positions), _ptr(cos_sin), cos_sin.shape[0], _ptr(slots), bs, _ptr(qa),
+                                  _ptr(cache) if dkv_off >= 0 else None, _stream(dev)))
+    return qa
+
+
+def latent_attention(qa: torch.Tensor, cache: torch.Tensor, batch: SeqBatch, R: int, scale: float, window: int = 0,
+                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Absorbed queries qa [T, H, R + dr] against the latent pool cache [nb, bs, R + dr]: the row at position p sees
+    positions j <= p (window > 0: and p - j < window); returns sigmoid(gate[t, h]) * sum_j p_j cache[j, :R] as
+    [T, H, R] of qa's dtype.  gate [T, H] may be a column slice of a wider row.  b2_latent_attention."""
+    lib = _lib.load()
+    dev = _need_cuda(qa=qa, cache=cache, gate=gate)
+    T, H, Dc = qa.shape
+    if not qa.is_contiguous() or cache.dtype != qa.dtype or cache.dim() != 3 or cache.shape[2] != Dc or not cache.is_contiguous():
+        raise ValueError("qa must be contiguous and cache [nb, bs, R + dr] of its dtype")
+    bt = batch.block_tables
+    if bt is None or bt.dtype != torch.int32 or bt.dim() != 2 or bt.stride(1) != 1 or bt.shape[0] < batch.n_seq \
+            or (bt.shape[0] > 1 and bt.stride(0) != bt.shape[1]):
+        raise ValueError("block_tables must be a contiguous int32 [n_seq, max_nb]")
+    gs = 0
+    if gate is not None:
+        if gate.dtype != qa.dtype or gate.dim() != 2 or tuple(gate.shape) != (T, H) or (H > 1 and gate.stride(1) != 1):
+            raise ValueError("gate must be [T, H] of qa's dtype with a contiguous last axis")
+        gs = gate.stride(0) if T > 1 else H
+    out = torch.empty(T, H, R, dtype=qa.dtype, device=dev)
+    _lib.check(lib.b2_latent_attention(_ptr(out), _ptr(qa), _ptr(cache), _act(qa, "qa"), _ptr(bt), bt.shape[1], _ptr(batch.cu_q),
+                                       _ptr(batch.ctx_start), batch.n_seq, T, H, R, Dc - R, cache.shape[1], float(scale),
+                                       int(window), _ptr(gate), gs, _stream(dev)))
+    return out

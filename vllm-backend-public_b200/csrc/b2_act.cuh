@@ -39,6 +39,12 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+// gated unit with both inputs bounded: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(alpha g') * (u' + 1)
+__device__ __forceinline__ float glu_clamped_f(float g, float u, float alpha, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoid_f(alpha * g) * (u + 1.f);
+}
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // Sequence of batch row `row` when rows are grouped by cu[0..n] (cu[0] = 0, cu[n] = rows in the batch).

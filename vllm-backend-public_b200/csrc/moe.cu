@@ -1,11 +1,14 @@
 // moe.cu -- a routed mixture of gated feed-forward experts over a token batch.
 //
-//   b2_moe_route     z = W_r h + b in fp32 (one warp per token), the `top` largest logits (lowest index wins a tie), weights =
-//                    softmax over the chosen logits only.
+//   b2_moe_route     z = W_r h in fp32 (one warp per token).  B2_ROUTE_TOPK_SOFTMAX: the `top` largest of z + b (lowest index
+//                    wins a tie), weights = softmax over the chosen logits only.  B2_ROUTE_SOFTMAX_ALL: s = softmax(z) over
+//                    all experts, the `top` largest of s + b are chosen, weights = their s (not renormalised).
 //   b2_moe_align     counting sort of the T*top (token, choice) pairs by expert into row tiles of kMoeBM rows: every tile
 //                    belongs to one expert, experts are padded to a tile boundary with -1.  Entirely on the device (no host
 //                    read of the counts), so the step stays capturable in a CUDA graph and never waits for the GPU.
-//   b2_moe_gate_up   per tile: act = SiLU(h W_gate[e]^T) * (h W_up[e]^T), rows gathered through the sorted list.
+//   b2_moe_gate_up   per tile: act = glu(h W_gate[e]^T, h W_up[e]^T), rows gathered through the sorted list.  glu(g, u) is
+//                    SiLU(g) * u (B2_GLU_SILU) or, with g' = min(g, limit) and u' = clamp(u, -limit, limit),
+//                    g' * sigmoid(alpha * g') * (u' + 1) (B2_GLU_CLAMPED).
 //   b2_moe_down      per tile: rows = act W_down[e]^T, fp32.
 //   b2_moe_combine   y[t] = sum_j weight[t, j] * rows[place of (t, j)], summed in choice order in fp32: a token's result
 //                    does not depend on what else is in the batch.
@@ -26,8 +29,8 @@ constexpr int kMoeBM = 32, kMoeBN = 64, kMoeBK = 32;
 // divides the L2 traffic of a prompt batch by TOK), then warp t picks the `top` largest of token t.
 template <typename T, int TOK>
 __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_r,
-                                 const float* __restrict__ bias, int rows, int D, int E, int top, bool vec, bool vec16,
-                                 int32_t* __restrict__ ids, float* __restrict__ wts) {
+                                 const float* __restrict__ bias, int rows, int D, int E, int top, int scoring, bool vec,
+                                 bool vec16, int32_t* __restrict__ ids, float* __restrict__ wts) {
     extern __shared__ float route_sm[];              // h [TOK][D] | z [TOK][E]
     float* hs = route_sm;
     float* zs = route_sm + (size_t)TOK * D;
@@ -84,13 +87,46 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, cons
 #pragma unroll
         for (int tt = 0; tt < TOK; ++tt) {
             const float v = b2::warp_sum(a[tt][0] + a[tt][1]);
-            if (lane == 0) zs[tt * E + e] = v + (bias ? bias[e] : 0.f);
+            if (lane == 0) zs[tt * E + e] = v + ((bias && scoring == B2_ROUTE_TOPK_SOFTMAX) ? bias[e] : 0.f);
         }
     }
     __syncthreads();
     for (int tt = wid; tt < nt; tt += nw) {
         float* z = zs + (size_t)tt * E;
         const int t = t0 + tt;
+        if (scoring == B2_ROUTE_SOFTMAX_ALL) {
+            // scores over all experts; the choice adds the correction, the weight is the plain score
+            float mx = -INFINITY;
+            for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+            mx = b2::warp_max(mx);
+            float den = 0.f;
+            for (int e = lane; e < E; e += 32) den += expf(z[e] - mx);
+            den = b2::warp_sum(den);
+            for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / den;
+            __syncwarp();
+            for (int j = 0; j < top; ++j) {
+                float best = -INFINITY;
+                int arg = 0x7fffffff;
+                for (int e = lane; e < E; e += 32) {
+                    const float c = z[e] + (bias ? bias[e] : 0.f);          // a chosen expert holds -inf
+                    if (c > best) { best = c; arg = e; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                    if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+                }
+                if (arg == 0x7fffffff) arg = 0;
+                if (lane == 0) {
+                    ids[(size_t)t * top + j] = arg;
+                    wts[(size_t)t * top + j] = z[arg] == -INFINITY ? 0.f : z[arg];
+                    z[arg] = -INFINITY;
+                }
+                __syncwarp();
+            }
+            continue;
+        }
         float v0 = 0.f, sum = 0.f;
         for (int j = 0; j < top; ++j) {
             float best = -INFINITY;
@@ -345,7 +381,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_gate, const T* __restrict__ w_up,
                    int64_t w13_expert_stride, const int32_t* __restrict__ sorted, const int32_t* __restrict__ tile_expert,
-                   int top, int D, int F, bool vec, T* __restrict__ act) {
+                   int top, int D, int F, bool vec, int glu, float alpha, float limit, T* __restrict__ act) {
     __shared__ __align__(128) unsigned char sm[TileSmem<T, 2>::BYTES];
     const float* c_sm = reinterpret_cast<const float*>(sm);
     const int e = tile_expert[blockIdx.x];
@@ -364,7 +400,7 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restric
         const int r = idx / kMoeBN, c = idx % kMoeBN;
         if (n0 + c < F && sorted[m0 + r] >= 0) {
             const float g = c_sm[idx], u = c_sm[kMoeBM * kMoeBN + idx];
-            b2::st(act + (size_t)(m0 + r) * F + n0 + c, b2::silu_f(g) * u);
+            b2::st(act + (size_t)(m0 + r) * F + n0 + c, glu == B2_GLU_CLAMPED ? b2::glu_clamped_f(g, u, alpha, limit) : b2::silu_f(g) * u);
         }
     }
 }
@@ -429,8 +465,10 @@ extern "C" int b2_moe_capacity(int n, int E) {
 }
 
 extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
-                            int D, int E, int top, int32_t* ids, float* weights, void* stream) {
+                            int D, int E, int top, int scoring, int32_t* ids, float* weights, void* stream) {
     B2_REQUIRE(T >= 0 && D > 0 && E > 0 && top >= 1 && top <= E, B2_EINVAL, "moe_route: bad sizes D=%d E=%d top=%d", D, E, top);
+    B2_REQUIRE(scoring == B2_ROUTE_TOPK_SOFTMAX || scoring == B2_ROUTE_SOFTMAX_ALL, B2_EINVAL, "moe_route: unknown scoring %d",
+               scoring);
     if (T == 0) return B2_OK;
     B2_REQUIRE(h && w_router && ids && weights, B2_EINVAL, "moe_route: null pointer");
     // prompt batches: four tokens share a CTA (and every weight load); small batches keep a CTA per token
@@ -446,12 +484,12 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
             auto kern = moe_route_kernel<A, 4>;
             if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             kern<<<(T + 3) / 4, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias,
-                                                        T, D, E, top, vec, vec16, ids, weights);
+                                                        T, D, E, top, scoring, vec, vec16, ids, weights);
         } else {
             auto kern = moe_route_kernel<A, 1>;
             if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             kern<<<T, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, T, D, E, top,
-                                              vec, vec16, ids, weights);
+                                              scoring, vec, vec16, ids, weights);
         }
     });
     B2_CUDA_OK(cudaGetLastError());
@@ -475,8 +513,9 @@ extern "C" int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gat
                               int64_t w13_expert_stride, int act_dtype, int T, int D, int F, int top, int cap,
                               const int32_t* sorted,
                               const int32_t* tile_expert, const int32_t* place, const float* weights, void* act, float* rows,
-                              void* y, int64_t y_stride, void* stream) {
+                              void* y, int64_t y_stride, int glu, float glu_alpha, float glu_limit, void* stream) {
     B2_REQUIRE(T >= 0 && D > 0 && F > 0 && top >= 1 && cap % kMoeBM == 0, B2_EINVAL, "moe_experts: bad sizes");
+    B2_REQUIRE(glu == B2_GLU_SILU || glu == B2_GLU_CLAMPED, B2_EINVAL, "moe_experts: unknown gated activation %d", glu);
     if (T == 0) return B2_OK;
     B2_REQUIRE(h && w_gate && w_up && w_down && sorted && tile_expert && place && weights && act && rows && y, B2_EINVAL,
                "moe_experts: null pointer");
@@ -490,7 +529,7 @@ extern "C" int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gat
     B2_DISPATCH_ACT(act_dtype, A, {
         moe_gate_up_kernel<A><<<dim3(tiles, (F + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
             static_cast<const A*>(h), h_stride, static_cast<const A*>(w_gate), static_cast<const A*>(w_up), w13_expert_stride,
-            sorted, tile_expert, top, D, F, vec1, static_cast<A*>(act));
+            sorted, tile_expert, top, D, F, vec1, glu, glu_alpha, glu_limit, static_cast<A*>(act));
         moe_down_kernel<A><<<dim3(tiles, (D + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
             static_cast<const A*>(act), static_cast<const A*>(w_down), sorted, tile_expert, D, F, vec2, rows);
         moe_combine_kernel<A, float><<<T, 256, 0, st>>>(rows, place, weights, top, D, static_cast<A*>(y), y_stride);

@@ -1,0 +1,180 @@
+// post_norm.cu -- the residual path of a decoder that normalises every sublayer on both sides ("sandwich" norms), and
+// the element-wise pieces of its feed-forwards and output:
+//
+//   b2_sandwich_norm   one pass over the fp32 residual rows x [T, D]:
+//                      (1) when y is given: the sublayer output is normalised and added, x' = x + norm(y; post_w, post_b)
+//                          (post_w NULL: plain x' = x + y);
+//                      (2) when h is given: the next sublayer's input is normalised out, h = norm(x'; pre_w, pre_b).
+//                      norm = layer norm (B2_NORM_LAYER, bias optional) or RMS norm (B2_NORM_RMS), eps inside the root.
+//                      The write-back and the next read-out touch the same row, so the op moves D*4 in, D*4 out for the
+//                      residual plus one activation row each way.  With post_w = NULL it is residual add + pre-norm.
+//   b2_relu_sq         out = max(in, 0)^2
+//   b2_glu_and_mul     out[t, i] = glu(in[t, i], in[t, I + i]) for rows [gate | up]: SiLU(g) * u (B2_GLU_SILU) or the bounded
+//                      unit g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit) (B2_GLU_CLAMPED)
+//   b2_softcap         z <- cap * tanh(z / cap) in place
+// The residual and all statistics are fp32 whatever the activation type.
+#include "b2_act.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+sandwich_norm_kernel(float* __restrict__ x, int D, const T* __restrict__ y, int64_t y_stride, const float* __restrict__ post_w,
+                     const float* __restrict__ post_b, const float* __restrict__ pre_w, const float* __restrict__ pre_b, float eps,
+                     int norm_kind, T* __restrict__ h, int64_t h_stride) {
+    extern __shared__ float row_sm[];                // [D]; a thread only ever touches its own columns
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    float* xt = x + (size_t)t * D;
+    const bool vec = D % 4 == 0;
+    float sum = 0.f;
+    if (y) {
+        const T* yt = y + (size_t)t * y_stride;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float v = b2::ld(yt + d);
+            row_sm[d] = v;
+            sum += v;
+        }
+        float mean = 0.f, inv = 1.f;
+        if (post_w) {
+            if (norm_kind == B2_NORM_LAYER) mean = b2::block_sum(sum, red) / (float)D;
+            float sq = 0.f;
+            for (int d = threadIdx.x; d < D; d += blockDim.x) {
+                const float c = row_sm[d] - mean;
+                sq = fmaf(c, c, sq);
+            }
+            inv = rsqrtf(b2::block_sum(sq, red) / (float)D + eps);
+        }
+        sum = 0.f;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            float v = row_sm[d];
+            if (post_w) v = (v - mean) * inv * post_w[d] + (post_b ? post_b[d] : 0.f);
+            v += xt[d];
+            xt[d] = v;
+            row_sm[d] = v;
+            sum += v;
+        }
+    } else {
+        if (vec) {
+            for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+                const float4 v = *reinterpret_cast<const float4*>(xt + d);
+                *reinterpret_cast<float4*>(row_sm + d) = v;
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+        } else {
+            for (int d = threadIdx.x; d < D; d += blockDim.x) {
+                row_sm[d] = xt[d];
+                sum += row_sm[d];
+            }
+        }
+    }
+    if (!h) return;
+    __syncthreads();                                 // the second pass may use another column mapping than the first
+    float mean = 0.f;
+    if (norm_kind == B2_NORM_LAYER) mean = b2::block_sum(sum, red) / (float)D;
+    float sq = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float c = row_sm[d] - mean;
+        sq = fmaf(c, c, sq);
+    }
+    const float inv = rsqrtf(b2::block_sum(sq, red) / (float)D + eps);
+    T* ho = h + (size_t)t * h_stride;
+    for (int d = threadIdx.x; d < D; d += blockDim.x)
+        b2::st(ho + d, (row_sm[d] - mean) * inv * pre_w[d] + (pre_b ? pre_b[d] : 0.f));
+}
+
+template <typename T>
+__global__ void relu_sq_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ in, int64_t in_stride, int I) {
+    const int t = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
+        const float v = fmaxf(b2::ld(in + (size_t)t * in_stride + i), 0.f);
+        b2::st(out + (size_t)t * out_stride + i, v * v);
+    }
+}
+
+template <typename T>
+__global__ void glu_and_mul_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ in, int64_t in_stride, int I,
+                                   int glu, float alpha, float limit) {
+    const int t = blockIdx.x;
+    const T* r = in + (size_t)t * in_stride;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
+        const float g = b2::ld(r + i), u = b2::ld(r + I + i);
+        b2::st(out + (size_t)t * out_stride + i, glu == B2_GLU_CLAMPED ? b2::glu_clamped_f(g, u, alpha, limit) : b2::silu_f(g) * u);
+    }
+}
+
+template <typename T>
+__global__ void softcap_kernel(T* __restrict__ z, int64_t stride, int V, float cap) {
+    const int t = blockIdx.x;
+    const float inv = 1.f / cap;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < V; i += gridDim.y * blockDim.x) {
+        T* p = z + (size_t)t * stride + i;
+        b2::st(p, cap * tanhf(b2::ld(p) * inv));
+    }
+}
+
+inline dim3 rows_grid(int cols, int rows) {
+    int gx = (cols + 255) / 256;
+    if (gx > 64) gx = 64;
+    return dim3(rows, gx);
+}
+
+}  // namespace
+
+extern "C" int b2_sandwich_norm(float* x, int T, int D, const void* y, int64_t y_stride, const float* post_w,
+                                const float* post_b, const float* pre_w, const float* pre_b, float eps, int norm_kind, void* h,
+                                int64_t h_stride, int act_dtype, void* stream) {
+    B2_REQUIRE(T >= 0 && D > 0, B2_EINVAL, "sandwich_norm: bad sizes T=%d D=%d", T, D);
+    if (T == 0 || (!y && !h)) return B2_OK;
+    B2_REQUIRE(x, B2_EINVAL, "sandwich_norm: null residual");
+    B2_REQUIRE(!h || pre_w, B2_EINVAL, "sandwich_norm: a read-out needs its norm weight");
+    B2_REQUIRE(norm_kind == B2_NORM_LAYER || norm_kind == B2_NORM_RMS, B2_EINVAL, "sandwich_norm: unknown norm kind %d", norm_kind);
+    const size_t smem = (size_t)D * sizeof(float);
+    B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "sandwich_norm: width %d does not fit shared memory", D);
+    B2_REQUIRE(b2_aligned16(x), B2_EINVAL, "sandwich_norm: the residual must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int threads = D >= 4096 ? 512 : (D >= 512 ? 256 : 128);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        auto kern = sandwich_norm_kernel<A>;
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<T, threads, smem, st>>>(x, D, static_cast<const A*>(y), y_stride, post_w, post_b, pre_w, pre_b, eps, norm_kind,
+                                       static_cast<A*>(h), h_stride);
+    });
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_relu_sq(void* out, int64_t out_stride, const void* in, int64_t in_stride, int act_dtype, int T, int I,
+                          void* stream) {
+    B2_REQUIRE(T >= 0 && I > 0, B2_EINVAL, "relu_sq: bad sizes T=%d I=%d", T, I);
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(out && in, B2_EINVAL, "relu_sq: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, (relu_sq_kernel<A><<<rows_grid(I, T), 256, 0, st>>>(static_cast<A*>(out), out_stride,
+                                                                                   static_cast<const A*>(in), in_stride, I)));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_glu_and_mul(void* out, int64_t out_stride, const void* gate_up, int64_t in_stride, int act_dtype, int T, int I,
+                              int glu, float alpha, float limit, void* stream) {
+    B2_REQUIRE(T >= 0 && I > 0, B2_EINVAL, "glu_and_mul: bad sizes T=%d I=%d", T, I);
+    B2_REQUIRE(glu == B2_GLU_SILU || glu == B2_GLU_CLAMPED, B2_EINVAL, "glu_and_mul: unknown gated activation %d", glu);
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(out && gate_up, B2_EINVAL, "glu_and_mul: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, (glu_and_mul_kernel<A><<<rows_grid(I, T), 256, 0, st>>>(
+        static_cast<A*>(out), out_stride, static_cast<const A*>(gate_up), in_stride, I, glu, alpha, limit)));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_softcap(void* z, int64_t stride, int act_dtype, int T, int V, float cap, void* stream) {
+    B2_REQUIRE(T >= 0 && V > 0 && cap > 0.f, B2_EINVAL, "softcap: bad sizes T=%d V=%d cap=%g", T, V, cap);
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(z, B2_EINVAL, "softcap: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, (softcap_kernel<A><<<rows_grid(V, T), 256, 0, st>>>(static_cast<A*>(z), stride, V, cap)));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
