@@ -77,27 +77,37 @@ def latent_kv(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float):
     return c, kr
 
 
+def windowed_attention(q, k, v, scale: float, window: int, first_pos: int = 0):
+    """q [Tq, H, dk] at positions first_pos .. first_pos + Tq - 1; k [Tk, H, dk], v [Tk, H, dv] at positions 0 .. Tk - 1.
+    Position i sees j with 0 <= i - j < window (window 0: every j <= i).  Ordinary softmax.  Returns [Tq, H, dv]."""
+    Tq, H, _ = q.shape
+    out = torch.zeros(Tq, H, v.shape[2], dtype=q.dtype)
+    for t in range(Tq):
+        i = first_pos + t
+        first = max(0, i - window + 1) if window else 0
+        for hh in range(H):
+            s = (k[first:i + 1, hh] @ q[t, hh]) * scale
+            pr = torch.softmax(s, 0)
+            out[t, hh] = pr @ v[first:i + 1, hh]
+    return out
+
+
 def latent_attention(h, m: dict, w: Dict[str, torch.Tensor], p: str, c, kr):
-    """h [T, D] -> [T, D].  Keys and values are rebuilt per head from the latent c; position i sees j with
-    0 <= i - j < window; head outputs are gated by sigmoid(W_g h)."""
+    """h [T, D] -> [T, D].  Keys and values are rebuilt per head from the latent c (key = [W_uk c | shared rotated part]);
+    head outputs are gated by sigmoid(W_g h)."""
     T = h.shape[0]
-    H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    H, dn, dr, dv = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
     rot = m["rot"]
     freqs, mag = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
     window = (m.get("mask") or {}).get("size") or 0
-    q = (h @ w[p + ".mix.q"].to(F64).T).view(T, H, dn + dr)
+    q = (h @ w[p + ".mix.q"].to(F64).T).view(T, H, dn + dr).clone()
+    for t in range(T):
+        q[t, :, dn:] = rotate(q[t, :, dn:], t, freqs, mag, rot["dims"])
     gate = torch.sigmoid(h @ w[p + ".mix.g"].to(F64).T)                      # [T, H]
     kn = (c @ w[p + ".mix.uk"].to(F64).T).view(T, H, dn)
+    k = torch.cat([kn, kr[:, None, :].expand(T, H, dr)], -1)
     v = (c @ w[p + ".mix.uv"].to(F64).T).view(T, H, dv)
-    out = torch.zeros(T, H, dv, dtype=F64)
-    for i in range(T):
-        first = max(0, i - window + 1) if window else 0
-        for hh in range(H):
-            qn = q[i, hh, :dn]
-            qr = rotate(q[i, hh, dn:], i, freqs, mag, rot["dims"])
-            s = torch.stack([(qn @ kn[j, hh] + qr @ kr[j]) * m["scale"] for j in range(first, i + 1)])
-            pr = torch.softmax(s, 0)
-            out[i, hh] = (pr[:, None] * v[first:i + 1, hh]).sum(0) * gate[i, hh]
+    out = windowed_attention(q, k, v, m["scale"], window) * gate[:, :, None]
     return out.reshape(T, H * dv) @ w[p + ".mix.o"].to(F64).T
 
 

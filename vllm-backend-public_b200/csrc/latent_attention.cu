@@ -148,6 +148,205 @@ __global__ void latent_attention_kernel(const T* __restrict__ qa, const T* __res
     }
 }
 
+// ------------------------------------------------------------------------------------------------- tensor-core kernel
+// bf16, latent size R in {64, 128, 256, 512}, rotated part a multiple of 16.  All heads read the same cache rows, so the
+// M side of the products is (token, head): one CTA takes kLQ = 64 rows = 64 / Hc consecutive tokens of one sequence x Hc
+// heads (Hc = min(H, 64)).  A decode row (one token) and a prompt portion are the same case with another token count.
+// Keys are walked 64 at a time from the first token's window start to the last token's position; a key tile is gathered
+// from the pages into shared memory ONCE per CTA (cp.async, 16 bytes per copy) and serves S = Q K^T over all R + dr columns
+// and O += P V over its first R columns (the value of a key is the head of its own row).  Eight warps: four groups of 16
+// rows x two halves of the R output columns; both halves compute the group's scores (mma.sync m16n8k16, ldmatrix operands)
+// and keep the online softmax in registers (exp2 with the scale folded in).  The gate multiplies the normalised output.
+constexpr int kLQ = 64, kLK = 64;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b2::smem_u32(dst)), "l"(src) : "memory");
+}
+
+template <int RT>
+__global__ void __launch_bounds__(256)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ cache,
+                            const int32_t* __restrict__ block_tables, int max_nb, const int32_t* __restrict__ cu_q,
+                            const int32_t* __restrict__ ctx_start, int n_seq, int H, int Hc, int dr, int bs, float scale_log2,
+                            int window, const __nv_bfloat16* __restrict__ gate, int64_t gate_stride,
+                            __nv_bfloat16* __restrict__ out) {
+    constexpr int R = 16 * RT;
+    const int Dc = R + dr, LD = Dc + 8, vecs = Dc / 8;
+    extern __shared__ __align__(16) unsigned char lat_smem[];
+    __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(lat_smem);       // [64][LD]
+    __nv_bfloat16* k_sm = q_sm + kLQ * LD;                                  // [64][LD]
+    __shared__ int s_info[2];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, wm = w & 3, wn = w >> 2;
+    const int Gt = kLQ / Hc;                                                // tokens per CTA
+    if (tid == 0) {
+        int want = blockIdx.x, found = -1, t0 = 0;
+        for (int s = 0; s < n_seq; ++s) {
+            const int nt = (cu_q[s + 1] - cu_q[s] + Gt - 1) / Gt;
+            if (want < nt) { found = s; t0 = want * Gt; break; }
+            want -= nt;
+        }
+        s_info[0] = found;
+        s_info[1] = t0;
+    }
+    __syncthreads();
+    const int seq = s_info[0], t0 = s_info[1];
+    if (seq < 0) return;
+    const int h0 = blockIdx.y * Hc, nh = min(Hc, H - h0);
+    const int tok0 = cu_q[seq] + t0;                                        // batch row of the CTA's first token
+    const int ntok = min(Gt, cu_q[seq + 1] - tok0);
+    const int ctx = ctx_start[seq];
+    if (ctx < 0) {                                                          // padding: zero rows
+        for (int idx = tid; idx < ntok * nh * (R / 8); idx += 256) {
+            const int rr = idx / (R / 8), c = (idx % (R / 8)) * 8;
+            *reinterpret_cast<uint4*>(out + ((size_t)(tok0 + rr / nh) * H + h0 + rr % nh) * R + c) = make_uint4(0, 0, 0, 0);
+        }
+        return;
+    }
+    const int p0 = ctx + t0, p_last = p0 + ntok - 1;
+    const int klo = window > 0 ? max(p0 - window + 1, 0) : 0;
+    const int32_t* bt = block_tables + (size_t)seq * max_nb;
+
+    for (int idx = tid; idx < kLQ * vecs; idx += 256) {
+        const int r = idx / vecs, c = (idx % vecs) * 8;
+        const int tk = r / Hc, hd = r % Hc;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tk < ntok && hd < nh) v = *reinterpret_cast<const uint4*>(qa + ((size_t)(tok0 + tk) * H + h0 + hd) * Dc + c);
+        *reinterpret_cast<uint4*>(q_sm + r * LD + c) = v;
+    }
+    const int gq = lane >> 2, tq = lane & 3;
+    const int ra = wm * 16 + gq, rb = ra + 8;                               // this thread's two rows
+    const int i0 = p0 + ra / Hc, i1 = p0 + rb / Hc;                         // their positions
+    const int lo0 = window > 0 ? max(i0 - window + 1, 0) : 0, lo1 = window > 0 ? max(i1 - window + 1, 0) : 0;
+    const int w_first = p0 + (wm * 16) / Hc, w_last = p0 + (wm * 16 + 15) / Hc;
+    const int w_lo = window > 0 ? max(w_first - window + 1, 0) : 0;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[RT][4];
+#pragma unroll
+    for (int n = 0; n < RT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const uint32_t q_base = b2::smem_u32(q_sm), k_base = b2::smem_u32(k_sm);
+    const int ksteps = Dc / 16;
+
+    for (int kv0 = klo; kv0 <= p_last; kv0 += kLK) {
+        __syncthreads();                                                    // the previous tile is consumed (and Q is stored)
+        for (int idx = tid; idx < kLK * vecs; idx += 256) {
+            const int key = idx / vecs, c = (idx % vecs) * 8, j = kv0 + key;
+            __nv_bfloat16* dst = k_sm + key * LD + c;
+            if (j <= p_last) cp_async16(dst, cache + ((size_t)bt[j / bs] * bs + j % bs) * Dc + c);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (kv0 > w_last || kv0 + kLK - 1 < w_lo) continue;                 // nothing in this tile is visible to the warp's rows
+        float sc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll 2
+        for (int kk = 0; kk < ksteps; ++kk) {
+            uint32_t a0, a1, a2, a3;
+            b2::ldmatrix_x4(q_base + 2u * ((wm * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                uint32_t b0, b1, b2_, b3;
+                const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), dim = kk * 16 + ((lane >> 3) & 1) * 8;
+                b2::ldmatrix_x4(k_base + 2u * (key * LD + dim), b0, b1, b2_, b3);
+                b2::mma_bf16_16816(sc[2 * n2], a0, a1, a2, a3, b0, b1);
+                b2::mma_bf16_16816(sc[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kv0 + n * 8 + 2 * tq + (e & 1);
+                const bool ok = e < 2 ? (j >= lo0 && j <= i0) : (j >= lo1 && j <= i1);
+                sc[n][e] = ok ? sc[n][e] * scale_log2 : -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = exp2f(m0 - mu0), c1 = exp2f(m1 - mu1);             // exp2(-inf) = 0: nothing accumulated yet
+        m0 = mn0;
+        m1 = mn1;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            sc[n][0] = exp2f(sc[n][0] - mu0);
+            sc[n][1] = exp2f(sc[n][1] - mu0);
+            sc[n][2] = exp2f(sc[n][2] - mu1);
+            sc[n][3] = exp2f(sc[n][3] - mu1);
+            s0 += sc[n][0] + sc[n][1];
+            s1 += sc[n][2] + sc[n][3];
+        }
+        l0 = l0 * c0 + s0;
+        l1 = l1 * c1 + s1;
+#pragma unroll
+        for (int n = 0; n < RT; ++n) {
+            o[n][0] *= c0;
+            o[n][1] *= c0;
+            o[n][2] *= c1;
+            o[n][3] *= c1;
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t a0 = b2::pack_bf16x2(sc[2 * ks][0], sc[2 * ks][1]), a1 = b2::pack_bf16x2(sc[2 * ks][2], sc[2 * ks][3]);
+            const uint32_t a2 = b2::pack_bf16x2(sc[2 * ks + 1][0], sc[2 * ks + 1][1]),
+                           a3 = b2::pack_bf16x2(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < RT / 2; ++n2) {
+                uint32_t b0, b1, b2_, b3;
+                const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = wn * (R / 2) + n2 * 16 + (lane >> 4) * 8;
+                b2::ldmatrix_x4_trans(k_base + 2u * (key * LD + col), b0, b1, b2_, b3);
+                b2::mma_bf16_16816(o[2 * n2], a0, a1, a2, a3, b0, b1);
+                b2::mma_bf16_16816(o[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int ta = ra / Hc, ha = ra % Hc, tb = rb / Hc, hb = rb % Hc;
+    const bool va = ta < ntok && ha < nh, vb = tb < ntok && hb < nh;
+    float f0 = l0 > 0.f ? 1.f / l0 : 0.f, f1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (gate) {
+        if (va) f0 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(tok0 + ta) * gate_stride + h0 + ha]));
+        if (vb) f1 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(tok0 + tb) * gate_stride + h0 + hb]));
+    }
+    __nv_bfloat16* oa = out + ((size_t)(tok0 + ta) * H + h0 + ha) * R + wn * (R / 2);
+    __nv_bfloat16* ob = out + ((size_t)(tok0 + tb) * H + h0 + hb) * R + wn * (R / 2);
+#pragma unroll
+    for (int n = 0; n < RT; ++n) {
+        const int col = n * 8 + 2 * tq;
+        if (va) *reinterpret_cast<uint32_t*>(oa + col) = b2::pack_bf16x2(o[n][0] * f0, o[n][1] * f0);
+        if (vb) *reinterpret_cast<uint32_t*>(ob + col) = b2::pack_bf16x2(o[n][2] * f1, o[n][3] * f1);
+    }
+}
+
+template <int RT>
+int launch_latent_mma(void* out, const void* qa, const void* cache, const int32_t* block_tables, int max_nb, const int32_t* cu_q,
+                      const int32_t* ctx_start, int n_seq, int T, int H, int dr, int bs, float scale, int window, const void* gate,
+                      int64_t gate_stride, cudaStream_t st) {
+    const int Dc = 16 * RT + dr, Hc = H < kLQ ? H : kLQ, Gt = kLQ / Hc;
+    const size_t smem = (size_t)(kLQ + kLK) * (Dc + 8) * sizeof(__nv_bfloat16);
+    auto kern = latent_attention_mma_kernel<RT>;
+    if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int tiles = T / Gt + n_seq;                       // upper bound on sum(ceil(len / Gt)); spare CTAs leave at once
+    kern<<<dim3(tiles, (H + Hc - 1) / Hc), 256, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(qa), static_cast<const __nv_bfloat16*>(cache), block_tables, max_nb, cu_q, ctx_start,
+        n_seq, H, Hc, dr, bs, scale * 1.4426950408889634f, window, static_cast<const __nv_bfloat16*>(gate), gate_stride,
+        static_cast<__nv_bfloat16*>(out));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
 }  // namespace
 
 extern "C" int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dtype, int T, int H, int dn, int dr, int rot_dims,
@@ -178,6 +377,17 @@ extern "C" int b2_latent_attention(void* out, const void* qa, const void* cache,
     if (T == 0 || n_seq == 0) return B2_OK;
     B2_REQUIRE(out && qa && cache && block_tables && cu_q && ctx_start, B2_EINVAL, "latent_attention: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (act_dtype == B2_ACT_BF16 && (R == 64 || R == 128 || R == 256 || R == 512) && dr % 16 == 0 && b2_aligned16(qa) &&
+        b2_aligned16(cache) && b2_aligned16(out) && (size_t)(kLQ + kLK) * (R + dr + 8) * 2 <= 227 * 1024) {
+#define B2_LAT(RT)                                                                                                            \
+    return launch_latent_mma<RT>(out, qa, cache, block_tables, max_nb, cu_q, ctx_start, n_seq, T, H, dr, bs, scale, window, gate, \
+                                 gate_stride, st)
+        if (R == 64) B2_LAT(4);
+        if (R == 128) B2_LAT(8);
+        if (R == 256) B2_LAT(16);
+        B2_LAT(32);
+#undef B2_LAT
+    }
     const int warps = 4;
     const size_t smem = (size_t)warps * (R + dr) * sizeof(float);
     B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "latent_attention: key size %d too large", R + dr);
