@@ -1,6 +1,6 @@
-"""`bench.py --family kofadra`: prefill and decode throughput of the Kofadra family at layer sizes of real models
+"""`bench.py --family kofadra|gatolix`: prefill and decode throughput of a model family at layer sizes of real models
 (random weights), beside the Llama model of equal width, heads, head size and ACTIVE feed-forward width, plus the device
-time of every new kernel with the roofline that bounds it beside the like kernel of the Llama path.
+time of every kernel of the family with the roofline that bounds it beside the like kernel of the Llama path.
 
 Both models run through the same engine (LLMEngine.replay_step: scheduler, pools, state slots, CUDA-graph decode).
   prefill   one prompt chunk of T tokens in one step; wall clock around the step (it ends with a stream synchronize)
@@ -21,6 +21,14 @@ SIZES = {
     # name: hidden, layers, heads, kv heads, head size, expert width, experts, chosen, vocabulary
     "2k": dict(hidden=2048, layers=4, heads=16, kv_heads=4, head_dim=128, ff=1024, experts=32, top=4, vocab=32000),
     "4k": dict(hidden=4096, layers=4, heads=32, kv_heads=8, head_dim=128, ff=1792, experts=64, top=8, vocab=32000),
+}
+
+# Gatolix: the latent geometry of the public DeepSeek-V2 family (512 + 64 numbers cached per token, heads of 128 + 64 / 128)
+GATOLIX_SIZES = {
+    "2k": dict(hidden=2048, layers=4, heads=16, kv_heads=4, dim=128, rot_dim=64, vdim=128, kv_rank=512, ff=1024, experts=32,
+               top=4, vocab=32000, window=1024),
+    "4k": dict(hidden=4096, layers=4, heads=32, kv_heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=512, ff=1792, experts=64,
+               top=8, vocab=32000, window=1024),
 }
 
 
@@ -93,7 +101,7 @@ def _time(fn, flush, iters=10):
     return statistics.median(ts)
 
 
-def _kernels(size, s, B, ctx, T):
+def _kernels_kofadra(size, s, B, ctx, T):
     """Device time of the new kernels and of the like Llama kernels on the same shapes."""
     import torch
     from b200attn import ops
@@ -177,23 +185,143 @@ def _kernels(size, s, B, ctx, T):
         torch.cuda.empty_cache()
 
 
+def _kernels_gatolix(size, s, B, ctx, T):
+    """Device time of the Gatolix kernels and of the like Llama kernels on the same shapes."""
+    import torch
+    from b200attn import ops
+    dev = torch.device("cuda", 0)
+    HBM, TF, src = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    D, H, G, F, E, top = s["hidden"], s["heads"], s["kv_heads"], s["ff"], s["experts"], s["top"]
+    dn, dr, dv, R, W = s["dim"], s["rot_dim"], s["vdim"], s["kv_rank"], s["window"]
+    Dc, d = R + dr, 128
+    bf = torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)          # noqa: E731
+
+    def line(kernel, phase, ms, bytes_=0, flops=0, like=None):
+        gbs, tfs = bytes_ / ms / 1e6, flops / ms / 1e9
+        _emit(bench="kernel", size=size, kernel=kernel, phase=phase, ms=round(ms, 4), gb_per_s=round(gbs, 1),
+              tflop_per_s=round(tfs, 2), frac_hbm=round(gbs / HBM, 3), frac_bf16=round(tfs / TF, 4), peaks=src, like=like)
+
+    tab = ops.rotary_table(ctx + T + 64, dr, 500000.0, {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}, dev)
+    for phase, n_seq, q_len, c in (("prefill", 1, T, 0), ("decode", B, 1, ctx)):
+        rows = n_seq * q_len
+        nb_seq = (c + q_len + 15) // 16
+        tables = torch.arange(n_seq * nb_seq, dtype=torch.int32, device=dev).view(n_seq, nb_seq)
+        batch = ops.SeqBatch(i32([i * q_len for i in range(n_seq + 1)]), i32([c] * n_seq), tables, None, n_seq, rows)
+        # ---- norm after the sublayer + residual + norm before the next  |  like: fused residual add + RMS norm
+        x = torch.randn(rows, D, device=dev)
+        y = torch.randn(rows, D, device=dev).to(bf)
+        ws = [torch.ones(D, device=dev) for _ in range(4)]
+        ms = _time(lambda: ops.sandwich_norm(x, y, *ws, eps=1e-6, h_dtype=bf), flush)
+        line("sandwich_norm (2 layer norms, fp32 residual)", phase, ms, bytes_=rows * D * (4 + 4 + 2 + 2), like="rms_norm")
+        res, wn = torch.randn(rows, D, device=dev).to(bf), torch.ones(D, device=dev).to(bf)
+        ms = _time(lambda: ops.rms_norm(y, wn, 1e-6, residual=res), flush)
+        line("rms_norm (Llama, bf16 residual)", phase, ms, bytes_=rows * D * 2 * 4)
+        # ---- rotation + pool write  |  like: rotary + KV write
+        P = H * (dn + dr) + H + Dc
+        proj = torch.randn(rows, P, device=dev).to(bf)
+        pos = (torch.arange(rows, device=dev) % q_len + c).to(torch.int32)
+        slots = (torch.arange(rows, device=dev) // q_len * (nb_seq * 16) + pos).to(torch.int64)
+        cache = torch.randn(n_seq * nb_seq, 16, Dc, device=dev).to(bf)
+        nw = torch.ones(R, device=dev)
+        g_off = H * (dn + dr)
+        ms = _time(lambda: ops.latent_prep(proj, H, dn, dr, dr, R, 0, g_off + H, nw, 1e-6, pos, tab, slots, cache), flush)
+        line("latent_prep (rotation + norm + pool write)", phase, ms, bytes_=rows * (H * dr * 4 + Dc * 4), like="rope_and_cache")
+        qkv = torch.randn(rows, (H + 2 * G) * d, device=dev).to(bf)
+        kc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        vc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        cos_sin = torch.randn(ctx + T + 64, d, device=dev)
+        ms = _time(lambda: ops.rope_and_cache(qkv, pos, cos_sin, kc, vc, slots, H), flush)
+        line("rope_and_cache (Llama)", phase, ms, bytes_=rows * ((H + G) * d * 4 + 2 * G * d * 4))
+        # ---- the per-head up-projections, carried to the query and to the output (library batched GEMMs)
+        qa = torch.randn(rows, H, Dc, device=dev).to(bf)
+        wuk = (torch.randn(H, dn, R, device=dev) * dn ** -0.5).to(bf)
+        wuv = (torch.randn(H, R, dv, device=dev) * R ** -0.5).to(bf)
+        qn = proj[:, :g_off].view(rows, H, dn + dr)[:, :, :dn].transpose(0, 1)
+        ol = torch.randn(rows, H, R, device=dev).to(bf)
+        ov = torch.empty(rows, H, dv, dtype=bf, device=dev)
+
+        def updown():
+            torch.bmm(qn, wuk, out=qa[:, :, :R].transpose(0, 1))
+            torch.bmm(ol.transpose(0, 1), wuv, out=ov.transpose(0, 1))
+        ms = _time(updown, flush)
+        line("query absorption + value up-projection (2 cuBLAS batched GEMMs)", phase, ms, flops=2 * rows * H * R * (dn + dv),
+             bytes_=H * R * (dn + dv) * 2 + rows * H * (dn + 2 * R + dv) * 2)
+        # ---- attention  |  like: tcgen05 prompt attention / paged decode
+        gate = proj[:, g_off:g_off + H]
+        ms = _time(lambda: ops.latent_attention(qa, cache, batch, R, 0.07, W, gate=gate), flush)
+        if phase == "prefill":
+            pairs = sum(min(p + 1, W) for p in range(T))                       # visible (query, key) pairs per head
+            line("latent_attention (window %d)" % W, phase, ms, flops=2 * pairs * H * (Dc + R), like="prefill_attention")
+            q = torch.randn(rows, H, d, device=dev).to(bf)
+            cu, cs = i32([0, T]), i32([0])
+            ms = _time(lambda: ops.prefill_attention(q, kc, vc, tables, cu, cs, total_tokens=T), flush)
+            line("prefill_attention (Llama, tcgen05, causal)", phase, ms, flops=4 * (T * (T + 1) // 2) * H * d)
+        else:
+            seen = min(W, c + 1)
+            line("latent_attention (window %d)" % W, phase, ms, bytes_=n_seq * seen * Dc * 2 + rows * H * (Dc + R) * 2,
+                 flops=2 * n_seq * seen * H * (Dc + R), like="paged_decode")
+            q = torch.randn(rows, H, d, device=dev).to(bf)
+            sl = i32([c + 1] * n_seq)
+            ms = _time(lambda: ops.paged_decode(q, kc, vc, tables, sl), flush)
+            line("paged_decode (Llama)", phase, ms, bytes_=n_seq * (c + 1) * G * 2 * d * 2)
+        # ---- dense feed-forward activation  |  like: silu_and_mul
+        a = torch.randn(rows, top * F, device=dev).to(bf)
+        ms = _time(lambda: ops.relu_sq(a), flush)
+        line("relu_sq", phase, ms, bytes_=rows * top * F * 4, like="silu_and_mul")
+        gu = torch.randn(rows, 2 * top * F, device=dev).to(bf)
+        ms = _time(lambda: ops.silu_and_mul(gu), flush)
+        line("silu_and_mul (Llama)", phase, ms, bytes_=rows * top * F * 6)
+        # ---- experts  |  like: the dense gated feed-forward of equal active width (two cuBLAS GEMMs + silu_and_mul)
+        h = torch.randn(rows, D, device=dev).to(bf)
+        wr, rb = (torch.randn(E, D, device=dev) * D ** -0.5).to(bf), torch.zeros(E, device=dev)
+        wgu = (torch.randn(E, 2 * F, D, device=dev) * D ** -0.5).to(bf)
+        wg, wu = wgu[:, :F], wgu[:, F:]
+        wd = (torch.randn(E, D, F, device=dev) * F ** -0.5).to(bf)
+        ms = _time(lambda: ops.moe_route(h, wr, rb, top, scoring=ops.ROUTE_SOFTMAX_ALL), flush)
+        line("moe_route (softmax over all + correction)", phase, ms, bytes_=rows * D * 2 + E * D * 2, flops=2 * rows * E * D)
+        ids, wts = ops.moe_route(h, wr, rb, top, scoring=ops.ROUTE_SOFTMAX_ALL)
+        ms = _time(lambda: ops.moe_experts(h, ids, wts, wg, wu, wd, w_gate_up=wgu, glu=ops.GLU_CLAMPED, glu_alpha=1.702,
+                                           glu_limit=7.0), flush)
+        used = min(E, rows * top)
+        path = "vendor grouped GEMM" if rows * top >= ops.MOE_GROUPED_GEMM_MIN_PAIRS else "own tiled kernels"
+        line(f"moe_experts, bounded units (sort + 2 grouped products + combine; {path})", phase, ms,
+             bytes_=used * 3 * F * D * 2, flops=6 * rows * top * F * D, like="dense gated MLP")
+        w1, w2 = (torch.randn(2 * top * F, D, device=dev) * D ** -0.5).to(bf), (torch.randn(D, top * F, device=dev) * 0.02).to(bf)
+        ms = _time(lambda: torch.nn.functional.linear(ops.silu_and_mul(torch.nn.functional.linear(h, w1)), w2), flush)
+        line("dense gated MLP (Llama: cuBLAS + silu_and_mul)", phase, ms, bytes_=3 * top * F * D * 2, flops=6 * rows * top * F * D)
+        # ---- soft cap on the sampled rows' logits
+        z = torch.randn(n_seq, s["vocab"], device=dev).to(bf)
+        ms = _time(lambda: ops.softcap_(z, 30.0), flush)
+        line("softcap", phase, ms, bytes_=n_seq * s["vocab"] * 4)
+        del wg, wu, wgu, wd, w1, w2, kc, vc, cache, qa, proj
+        torch.cuda.empty_cache()
+
+
 def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
     import torch
-    from b200attn.kofadra import bench_config
     from b200attn.model import ModelConfig
-    if family != "kofadra":
+    if family not in ("kofadra", "gatolix"):
         raise SystemExit(f"unknown family {family!r}")
-    B, ctx, T = 64, 2560, 4096          # ctx: 2.5 mask blocks of the bench geometry, so a decode row sees 513 keys
+    B, ctx, T = 64, 2560, 4096          # ctx: 2.5 mask blocks / windows of the bench geometries
     for name in sizes:
-        s = SIZES[name]
-        kcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"], s["top"],
-                            s["vocab"], name=f"kofadra-{name}")
+        if family == "kofadra":
+            from b200attn.kofadra import bench_config
+            s = SIZES[name]
+            fcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"],
+                                s["top"], s["vocab"], name=f"kofadra-{name}")
+        else:
+            from b200attn.gatolix import bench_config
+            s = GATOLIX_SIZES[name]
+            fcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["dim"], s["rot_dim"], s["vdim"], s["kv_rank"], s["ff"],
+                                s["experts"], s["top"], s["vocab"], window=s["window"], name=f"gatolix-{name}")
         lcfg = ModelConfig(f"llama-{name}", s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["top"] * s["ff"], s["vocab"],
                            max_position=8192)
-        _emit(bench="config", size=name, **s, kofadra_params=kcfg.params, llama_params=lcfg.params, prefill_tokens=T,
+        _emit(bench="config", size=name, **s, **{f"{family}_params": fcfg.params}, llama_params=lcfg.params, prefill_tokens=T,
               decode_batch=B, decode_ctx=ctx, data="synthetic", dtype="bf16")
-        _throughput(kcfg.name, kcfg, B, ctx, T, steps)
+        _throughput(fcfg.name, fcfg, B, ctx, T, steps)
         _throughput(lcfg.name, lcfg, B, ctx, T, steps)
         if kernels:
-            _kernels(name, s, B, ctx, T)
+            (_kernels_kofadra if family == "kofadra" else _kernels_gatolix)(name, s, B, ctx, T)
         torch.cuda.empty_cache()

@@ -162,7 +162,7 @@ def _attend(cuda, dt, H, Rk, dr, window, seqs, bs=16, loud=(), seed=0):
     return got, torch.cat(wants)
 
 
-SHAPES = [(3, 36, 12), (16, 64, 16), (8, 128, 32), (5, 64, 16), (2, 256, 64), (20, 64, 32)]
+SHAPES = [(3, 36, 12), (16, 64, 16), (8, 128, 32), (5, 64, 16), (2, 256, 64), (20, 64, 32), (72, 64, 16), (4, 512, 64)]
 
 
 @pytest.mark.parametrize("dt", DTYPES)

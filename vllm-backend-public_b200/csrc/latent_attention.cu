@@ -153,7 +153,8 @@ __global__ void latent_attention_kernel(const T* __restrict__ qa, const T* __res
 // M side of the products is (token, head): one CTA takes kLQ = 64 rows = 64 / Hc consecutive tokens of one sequence x Hc
 // heads (Hc = min(H, 64)).  A decode row (one token) and a prompt portion are the same case with another token count.
 // Keys are walked 64 at a time from the first token's window start to the last token's position; a key tile is gathered
-// from the pages into shared memory ONCE per CTA (cp.async, 16 bytes per copy) and serves S = Q K^T over all R + dr columns
+// from the pages into shared memory ONCE per CTA (cp.async, 16 bytes per copy, the next tile in flight while this one is
+// multiplied when two tiles fit beside Q) and serves S = Q K^T over all R + dr columns
 // and O += P V over its first R columns (the value of a key is the head of its own row).  Eight warps: four groups of 16
 // rows x two halves of the R output columns; both halves compute the group's scores (mma.sync m16n8k16, ldmatrix operands)
 // and keep the online softmax in registers (exp2 with the scale folded in).  The gate multiplies the normalised output.
@@ -168,13 +169,13 @@ __global__ void __launch_bounds__(256)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ cache,
                             const int32_t* __restrict__ block_tables, int max_nb, const int32_t* __restrict__ cu_q,
                             const int32_t* __restrict__ ctx_start, int n_seq, int H, int Hc, int dr, int bs, float scale_log2,
-                            int window, const __nv_bfloat16* __restrict__ gate, int64_t gate_stride,
+                            int window, int stages, const __nv_bfloat16* __restrict__ gate, int64_t gate_stride,
                             __nv_bfloat16* __restrict__ out) {
     constexpr int R = 16 * RT;
     const int Dc = R + dr, LD = Dc + 8, vecs = Dc / 8;
     extern __shared__ __align__(16) unsigned char lat_smem[];
     __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(lat_smem);       // [64][LD]
-    __nv_bfloat16* k_sm = q_sm + kLQ * LD;                                  // [64][LD]
+    __nv_bfloat16* k_sm = q_sm + kLQ * LD;                                  // [stages][64][LD]
     __shared__ int s_info[2];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, wm = w & 3, wn = w >> 2;
     const int Gt = kLQ / Hc;                                                // tokens per CTA
@@ -223,91 +224,109 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
     float o[RT][4];
 #pragma unroll
     for (int n = 0; n < RT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-    const uint32_t q_base = b2::smem_u32(q_sm), k_base = b2::smem_u32(k_sm);
+    const uint32_t q_base = b2::smem_u32(q_sm), k_base0 = b2::smem_u32(k_sm);
     const int ksteps = Dc / 16;
 
-    for (int kv0 = klo; kv0 <= p_last; kv0 += kLK) {
-        __syncthreads();                                                    // the previous tile is consumed (and Q is stored)
-        for (int idx = tid; idx < kLK * vecs; idx += 256) {
-            const int key = idx / vecs, c = (idx % vecs) * 8, j = kv0 + key;
-            __nv_bfloat16* dst = k_sm + key * LD + c;
-            if (j <= p_last) cp_async16(dst, cache + ((size_t)bt[j / bs] * bs + j % bs) * Dc + c);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    // a thread copies a quarter of one key row per tile: one page lookup, then 16-byte copies 64 bytes apart
+    const int ld_key = tid >> 2, ld_sub = (tid & 3) * 8;
+    auto issue = [&](int kv0, int buf) {
+        const int j = kv0 + ld_key;
+        __nv_bfloat16* dst = k_sm + (size_t)buf * kLK * LD + ld_key * LD;
+        if (j <= p_last) {
+            const __nv_bfloat16* src = cache + ((size_t)bt[j / bs] * bs + j % bs) * Dc;
+            for (int c = ld_sub; c < Dc; c += 32) cp_async16(dst + c, src + c);
+        } else {
+            for (int c = ld_sub; c < Dc; c += 32) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        if (kv0 > w_last || kv0 + kLK - 1 < w_lo) continue;                 // nothing in this tile is visible to the warp's rows
-        float sc[8][4];
+    };
+    const bool active = wm * 16 < ntok * Hc;                                // a row group without rows only helps to copy
+    const int ntiles = (p_last - klo) / kLK + 1;
+    issue(klo, 0);
+    for (int t = 0; t < ntiles; ++t) {
+        const int kv0 = klo + t * kLK, buf = stages == 2 ? (t & 1) : 0;
+        if (stages == 2 && t + 1 < ntiles) {                                // the next tile streams in while this one is multiplied
+            issue(kv0 + kLK, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();                                                    // the tile (and, first time, Q) is in shared memory
+        const uint32_t k_base = k_base0 + (uint32_t)buf * kLK * LD * 2u;
+        if (active && !(kv0 > w_last || kv0 + kLK - 1 < w_lo)) {            // else nothing in this tile is visible to the warp's rows
+            float sc[8][4];
 #pragma unroll
-        for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+            for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
 #pragma unroll 2
-        for (int kk = 0; kk < ksteps; ++kk) {
-            uint32_t a0, a1, a2, a3;
-            b2::ldmatrix_x4(q_base + 2u * ((wm * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+            for (int kk = 0; kk < ksteps; ++kk) {
+                uint32_t a0, a1, a2, a3;
+                b2::ldmatrix_x4(q_base + 2u * ((wm * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
 #pragma unroll
-            for (int n2 = 0; n2 < 4; ++n2) {
-                uint32_t b0, b1, b2_, b3;
-                const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), dim = kk * 16 + ((lane >> 3) & 1) * 8;
-                b2::ldmatrix_x4(k_base + 2u * (key * LD + dim), b0, b1, b2_, b3);
-                b2::mma_bf16_16816(sc[2 * n2], a0, a1, a2, a3, b0, b1);
-                b2::mma_bf16_16816(sc[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+                for (int n2 = 0; n2 < 4; ++n2) {
+                    uint32_t b0, b1, b2_, b3;
+                    const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), dim = kk * 16 + ((lane >> 3) & 1) * 8;
+                    b2::ldmatrix_x4(k_base + 2u * (key * LD + dim), b0, b1, b2_, b3);
+                    b2::mma_bf16_16816(sc[2 * n2], a0, a1, a2, a3, b0, b1);
+                    b2::mma_bf16_16816(sc[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = kv0 + n * 8 + 2 * tq + (e & 1);
+                    const bool ok = e < 2 ? (j >= lo0 && j <= i0) : (j >= lo1 && j <= i1);
+                    sc[n][e] = ok ? sc[n][e] * scale_log2 : -INFINITY;
+                }
+                mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float c0 = exp2f(m0 - mu0), c1 = exp2f(m1 - mu1);             // exp2(-inf) = 0: nothing accumulated yet
+            m0 = mn0;
+            m1 = mn1;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                sc[n][0] = exp2f(sc[n][0] - mu0);
+                sc[n][1] = exp2f(sc[n][1] - mu0);
+                sc[n][2] = exp2f(sc[n][2] - mu1);
+                sc[n][3] = exp2f(sc[n][3] - mu1);
+                s0 += sc[n][0] + sc[n][1];
+                s1 += sc[n][2] + sc[n][3];
+            }
+            l0 = l0 * c0 + s0;
+            l1 = l1 * c1 + s1;
+#pragma unroll
+            for (int n = 0; n < RT; ++n) {
+                o[n][0] *= c0;
+                o[n][1] *= c0;
+                o[n][2] *= c1;
+                o[n][3] *= c1;
+            }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const uint32_t a0 = b2::pack_bf16x2(sc[2 * ks][0], sc[2 * ks][1]), a1 = b2::pack_bf16x2(sc[2 * ks][2], sc[2 * ks][3]);
+                const uint32_t a2 = b2::pack_bf16x2(sc[2 * ks + 1][0], sc[2 * ks + 1][1]),
+                               a3 = b2::pack_bf16x2(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < RT / 2; ++n2) {
+                    uint32_t b0, b1, b2_, b3;
+                    const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = wn * (R / 2) + n2 * 16 + (lane >> 4) * 8;
+                    b2::ldmatrix_x4_trans(k_base + 2u * (key * LD + col), b0, b1, b2_, b3);
+                    b2::mma_bf16_16816(o[2 * n2], a0, a1, a2, a3, b0, b1);
+                    b2::mma_bf16_16816(o[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+                }
             }
         }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = kv0 + n * 8 + 2 * tq + (e & 1);
-                const bool ok = e < 2 ? (j >= lo0 && j <= i0) : (j >= lo1 && j <= i1);
-                sc[n][e] = ok ? sc[n][e] * scale_log2 : -INFINITY;
-            }
-            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
-            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float c0 = exp2f(m0 - mu0), c1 = exp2f(m1 - mu1);             // exp2(-inf) = 0: nothing accumulated yet
-        m0 = mn0;
-        m1 = mn1;
-        float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            sc[n][0] = exp2f(sc[n][0] - mu0);
-            sc[n][1] = exp2f(sc[n][1] - mu0);
-            sc[n][2] = exp2f(sc[n][2] - mu1);
-            sc[n][3] = exp2f(sc[n][3] - mu1);
-            s0 += sc[n][0] + sc[n][1];
-            s1 += sc[n][2] + sc[n][3];
-        }
-        l0 = l0 * c0 + s0;
-        l1 = l1 * c1 + s1;
-#pragma unroll
-        for (int n = 0; n < RT; ++n) {
-            o[n][0] *= c0;
-            o[n][1] *= c0;
-            o[n][2] *= c1;
-            o[n][3] *= c1;
-        }
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t a0 = b2::pack_bf16x2(sc[2 * ks][0], sc[2 * ks][1]), a1 = b2::pack_bf16x2(sc[2 * ks][2], sc[2 * ks][3]);
-            const uint32_t a2 = b2::pack_bf16x2(sc[2 * ks + 1][0], sc[2 * ks + 1][1]),
-                           a3 = b2::pack_bf16x2(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
-#pragma unroll
-            for (int n2 = 0; n2 < RT / 2; ++n2) {
-                uint32_t b0, b1, b2_, b3;
-                const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = wn * (R / 2) + n2 * 16 + (lane >> 4) * 8;
-                b2::ldmatrix_x4_trans(k_base + 2u * (key * LD + col), b0, b1, b2_, b3);
-                b2::mma_bf16_16816(o[2 * n2], a0, a1, a2, a3, b0, b1);
-                b2::mma_bf16_16816(o[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
-            }
-        }
+        __syncthreads();                                                    // the tile is consumed: its buffer may be refilled
+        if (stages == 1 && t + 1 < ntiles) issue(kv0 + kLK, 0);
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -335,13 +354,15 @@ int launch_latent_mma(void* out, const void* qa, const void* cache, const int32_
                       const int32_t* ctx_start, int n_seq, int T, int H, int dr, int bs, float scale, int window, const void* gate,
                       int64_t gate_stride, cudaStream_t st) {
     const int Dc = 16 * RT + dr, Hc = H < kLQ ? H : kLQ, Gt = kLQ / Hc;
-    const size_t smem = (size_t)(kLQ + kLK) * (Dc + 8) * sizeof(__nv_bfloat16);
+    const size_t tile = (size_t)kLK * (Dc + 8) * sizeof(__nv_bfloat16);
+    const int stages = 3 * tile <= 227 * 1024 - 64 ? 2 : 1;                 // two key tiles in flight when they fit beside Q
+    const size_t smem = (size_t)(1 + stages) * tile;
     auto kern = latent_attention_mma_kernel<RT>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int tiles = T / Gt + n_seq;                       // upper bound on sum(ceil(len / Gt)); spare CTAs leave at once
     kern<<<dim3(tiles, (H + Hc - 1) / Hc), 256, smem, st>>>(
         static_cast<const __nv_bfloat16*>(qa), static_cast<const __nv_bfloat16*>(cache), block_tables, max_nb, cu_q, ctx_start,
-        n_seq, H, Hc, dr, bs, scale * 1.4426950408889634f, window, static_cast<const __nv_bfloat16*>(gate), gate_stride,
+        n_seq, H, Hc, dr, bs, scale * 1.4426950408889634f, window, stages, static_cast<const __nv_bfloat16*>(gate), gate_stride,
         static_cast<__nv_bfloat16*>(out));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;

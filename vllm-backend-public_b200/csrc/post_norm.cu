@@ -17,78 +17,118 @@
 
 namespace {
 
-template <typename T>
+// four consecutive elements of an activation row (8 or 16 bytes, aligned)
+__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(b2::pack_bf16x2(v[0], v[1]), b2::pack_bf16x2(v[2], v[3]));
+}
+
+// W = 4: every access is a 16-byte (fp32) or 8-byte (bf16) vector; W = 1: any width and alignment.  A thread keeps to its
+// own columns in every pass, so the row in shared memory needs no barrier beyond those of the reductions.
+template <typename T, int W>
 __global__ void __launch_bounds__(512)
 sandwich_norm_kernel(float* __restrict__ x, int D, const T* __restrict__ y, int64_t y_stride, const float* __restrict__ post_w,
                      const float* __restrict__ post_b, const float* __restrict__ pre_w, const float* __restrict__ pre_b, float eps,
                      int norm_kind, T* __restrict__ h, int64_t h_stride) {
-    extern __shared__ float row_sm[];                // [D]; a thread only ever touches its own columns
+    extern __shared__ __align__(16) float row_sm[];  // [D]
     __shared__ float red[33];
     const int t = blockIdx.x;
     float* xt = x + (size_t)t * D;
-    const bool vec = D % 4 == 0;
+    const int step = blockDim.x * W;
     float sum = 0.f;
     if (y) {
         const T* yt = y + (size_t)t * y_stride;
-        for (int d = threadIdx.x; d < D; d += blockDim.x) {
-            const float v = b2::ld(yt + d);
-            row_sm[d] = v;
-            sum += v;
+        for (int d = threadIdx.x * W; d < D; d += step) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (W == 4) ld4(yt + d, v); else v[0] = b2::ld(yt + d);
+#pragma unroll
+            for (int c = 0; c < W; ++c) {
+                row_sm[d + c] = v[c];
+                sum += v[c];
+            }
         }
         float mean = 0.f, inv = 1.f;
         if (post_w) {
             if (norm_kind == B2_NORM_LAYER) mean = b2::block_sum(sum, red) / (float)D;
             float sq = 0.f;
-            for (int d = threadIdx.x; d < D; d += blockDim.x) {
-                const float c = row_sm[d] - mean;
-                sq = fmaf(c, c, sq);
+            for (int d = threadIdx.x * W; d < D; d += step) {
+#pragma unroll
+                for (int c = 0; c < W; ++c) {
+                    const float e = row_sm[d + c] - mean;
+                    sq = fmaf(e, e, sq);
+                }
             }
             inv = rsqrtf(b2::block_sum(sq, red) / (float)D + eps);
         }
         sum = 0.f;
-        for (int d = threadIdx.x; d < D; d += blockDim.x) {
-            float v = row_sm[d];
-            if (post_w) v = (v - mean) * inv * post_w[d] + (post_b ? post_b[d] : 0.f);
-            v += xt[d];
-            xt[d] = v;
-            row_sm[d] = v;
-            sum += v;
+        for (int d = threadIdx.x * W; d < D; d += step) {
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
+            if (W == 4) ld4(xt + d, r); else r[0] = xt[d];
+#pragma unroll
+            for (int c = 0; c < W; ++c) {
+                float v = row_sm[d + c];
+                if (post_w) v = (v - mean) * inv * post_w[d + c] + (post_b ? post_b[d + c] : 0.f);
+                r[c] += v;
+                row_sm[d + c] = r[c];
+                sum += r[c];
+            }
+            if (W == 4) st4(xt + d, r); else xt[d] = r[0];
         }
     } else {
-        if (vec) {
-            for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
-                const float4 v = *reinterpret_cast<const float4*>(xt + d);
-                *reinterpret_cast<float4*>(row_sm + d) = v;
-                sum += (v.x + v.y) + (v.z + v.w);
-            }
-        } else {
-            for (int d = threadIdx.x; d < D; d += blockDim.x) {
-                row_sm[d] = xt[d];
-                sum += row_sm[d];
+        for (int d = threadIdx.x * W; d < D; d += step) {
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
+            if (W == 4) ld4(xt + d, r); else r[0] = xt[d];
+#pragma unroll
+            for (int c = 0; c < W; ++c) {
+                row_sm[d + c] = r[c];
+                sum += r[c];
             }
         }
     }
     if (!h) return;
-    __syncthreads();                                 // the second pass may use another column mapping than the first
     float mean = 0.f;
     if (norm_kind == B2_NORM_LAYER) mean = b2::block_sum(sum, red) / (float)D;
     float sq = 0.f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float c = row_sm[d] - mean;
-        sq = fmaf(c, c, sq);
+    for (int d = threadIdx.x * W; d < D; d += step) {
+#pragma unroll
+        for (int c = 0; c < W; ++c) {
+            const float e = row_sm[d + c] - mean;
+            sq = fmaf(e, e, sq);
+        }
     }
     const float inv = rsqrtf(b2::block_sum(sq, red) / (float)D + eps);
     T* ho = h + (size_t)t * h_stride;
-    for (int d = threadIdx.x; d < D; d += blockDim.x)
-        b2::st(ho + d, (row_sm[d] - mean) * inv * pre_w[d] + (pre_b ? pre_b[d] : 0.f));
+    for (int d = threadIdx.x * W; d < D; d += step) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < W; ++c) v[c] = (row_sm[d + c] - mean) * inv * pre_w[d + c] + (pre_b ? pre_b[d + c] : 0.f);
+        if (W == 4) st4(ho + d, v); else b2::st(ho + d, v[0]);
+    }
 }
 
-template <typename T>
+template <typename T, int W>
 __global__ void relu_sq_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ in, int64_t in_stride, int I) {
     const int t = blockIdx.x;
-    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
-        const float v = fmaxf(b2::ld(in + (size_t)t * in_stride + i), 0.f);
-        b2::st(out + (size_t)t * out_stride + i, v * v);
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * W; i < I; i += gridDim.y * blockDim.x * W) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (W == 4) ld4(in + (size_t)t * in_stride + i, v); else v[0] = b2::ld(in + (size_t)t * in_stride + i);
+#pragma unroll
+        for (int c = 0; c < W; ++c) {
+            v[c] = fmaxf(v[c], 0.f);
+            v[c] *= v[c];
+        }
+        if (W == 4) st4(out + (size_t)t * out_stride + i, v); else b2::st(out + (size_t)t * out_stride + i, v[0]);
     }
 }
 
@@ -133,13 +173,20 @@ extern "C" int b2_sandwich_norm(float* x, int T, int D, const void* y, int64_t y
     B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "sandwich_norm: width %d does not fit shared memory", D);
     B2_REQUIRE(b2_aligned16(x), B2_EINVAL, "sandwich_norm: the residual must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int threads = D >= 4096 ? 512 : (D >= 512 ? 256 : 128);
+    const int threads = D >= 8192 ? 512 : (D >= 1024 ? 256 : 128);
+    const bool vec = D % 4 == 0 && (!y || (y_stride % 4 == 0 && b2_aligned16(y))) && (!h || (h_stride % 4 == 0 && b2_aligned16(h)));
+#define B2_SANDWICH(W)                                                                                                      \
+    do {                                                                                                                    \
+        auto kern = sandwich_norm_kernel<A, W>;                                                                             \
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        kern<<<T, threads, smem, st>>>(x, D, static_cast<const A*>(y), y_stride, post_w, post_b, pre_w, pre_b, eps, norm_kind, \
+                                       static_cast<A*>(h), h_stride);                                                       \
+    } while (0)
     B2_DISPATCH_ACT(act_dtype, A, {
-        auto kern = sandwich_norm_kernel<A>;
-        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<T, threads, smem, st>>>(x, D, static_cast<const A*>(y), y_stride, post_w, post_b, pre_w, pre_b, eps, norm_kind,
-                                       static_cast<A*>(h), h_stride);
+        if (vec) B2_SANDWICH(4);
+        else B2_SANDWICH(1);
     });
+#undef B2_SANDWICH
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
@@ -150,8 +197,11 @@ extern "C" int b2_relu_sq(void* out, int64_t out_stride, const void* in, int64_t
     if (T == 0) return B2_OK;
     B2_REQUIRE(out && in, B2_EINVAL, "relu_sq: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    B2_DISPATCH_ACT(act_dtype, A, (relu_sq_kernel<A><<<rows_grid(I, T), 256, 0, st>>>(static_cast<A*>(out), out_stride,
-                                                                                   static_cast<const A*>(in), in_stride, I)));
+    const bool vec = I % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && b2_aligned16(in) && b2_aligned16(out);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        if (vec) relu_sq_kernel<A, 4><<<rows_grid(I / 4, T), 256, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(in), in_stride, I);
+        else relu_sq_kernel<A, 1><<<rows_grid(I, T), 256, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(in), in_stride, I);
+    });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
