@@ -536,7 +536,9 @@ B2_API int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dtype, 
 B2_API int b2_latent_attention(void* out, const void* qa, const void* cache, int act_dtype, const int32_t* block_tables,
                                int max_nb, const int32_t* cu_q, const int32_t* ctx_start, int n_seq, int T, int H, int R,
                                int dr, int bs, float scale, int window /* 0: causal */, const void* gate /* or NULL */,
-                               int64_t gate_stride, void* stream);
+                               int64_t gate_stride, float* workspace /* or NULL */, int64_t workspace_floats, void* stream);
+B2_API int64_t b2_latent_attention_workspace(int act_dtype, int T, int n_seq, int H, int R, int dr, int bs, int window,
+                                             int max_nb);
 
 #ifdef __cplusplus
 }

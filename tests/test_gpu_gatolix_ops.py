@@ -176,6 +176,26 @@ def test_latent_attention_prompts_and_single_rows(cuda, dt, H, Rk, dr, window):
 
 
 @pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,Rk,dr", [(8, 128, 32), (2, 256, 64), (4, 512, 64), (20, 128, 16), (16, 64, 16), (3, 36, 12)])
+@pytest.mark.parametrize("window", [0, 1, 16, 37, 300])
+def test_latent_attention_decode_batches(cuda, dt, H, Rk, dr, window):
+    """Batches in which every sequence brings one row (what a decode step is): few rows, so the keys of a row are shared
+    out over warps and CTAs.  Contexts from nothing to several hundred tokens, one loud key at each window's first and
+    last-but-one position."""
+    seqs = [(0, 1), (1, 1), (15, 1), (16, 1), (63, 1), (64, 1), (65, 1), (200, 1), (511, 1), (640, 1)]
+    loud = []
+    for i, (nctx, _) in enumerate(seqs):
+        if window and nctx - window + 1 >= 0 and i % 2 == 0:
+            loud.append((i, 0, nctx - window + 1, 9.0))                       # the last key the window keeps
+        elif window and nctx - window >= 0:
+            loud.append((i, 0, nctx - window, 9.0))                           # the first key it has dropped
+    got, want = _attend(cuda, dt, H, Rk, dr, window, seqs, loud=loud, seed=window + H)
+    _close(got, want, dt, f"decode batch H={H} R={Rk} dr={dr} window={window}")
+    got, want = _attend(cuda, dt, H, Rk, dr, window, seqs[6:8], seed=5)       # two rows: more shares per row
+    _close(got, want, dt, "small decode batch")
+
+
+@pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("H,Rk,dr", [(3, 36, 12), (16, 64, 16), (8, 128, 32)])
 @pytest.mark.parametrize("edge", ["inside", "outside"])
 def test_latent_attention_loud_key_at_the_window_edge(cuda, dt, H, Rk, dr, edge):

@@ -127,7 +127,9 @@ SIGNATURES = {
     "b2_glu_and_mul": (i32, [vp, i64, vp, i64, i32, i32, i32, i32, f32, f32, vp]),
     "b2_softcap": (i32, [vp, i64, i32, i32, i32, f32, vp]),
     "b2_latent_prep": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp, vp, vp]),
-    "b2_latent_attention": (i32, [vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp, i64, vp]),
+    "b2_latent_attention": (i32, [vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp, i64, vp, i64,
+                                  vp]),
+    "b2_latent_attention_workspace": (i64, [i32, i32, i32, i32, i32, i32, i32, i32, i32]),
 }
 
 _lib = None

@@ -1063,7 +1063,10 @@ def latent_attention(qa: torch.Tensor, cache: torch.Tensor, batch: SeqBatch, R: 
             raise ValueError("gate must be [T, H] of qa's dtype with a contiguous last axis")
         gs = gate.stride(0) if T > 1 else H
     out = torch.empty(T, H, R, dtype=qa.dtype, device=dev)
+    # a batch too small to fill the GPU (decode rows) splits every row's keys over several CTAs and merges: fp32 scratch
+    nws = lib.b2_latent_attention_workspace(_act(qa, "qa"), T, batch.n_seq, H, R, Dc - R, cache.shape[1], int(window), bt.shape[1])
+    ws = torch.empty(nws, dtype=torch.float32, device=dev) if nws else None
     _lib.check(lib.b2_latent_attention(_ptr(out), _ptr(qa), _ptr(cache), _act(qa, "qa"), _ptr(bt), bt.shape[1], _ptr(batch.cu_q),
                                        _ptr(batch.ctx_start), batch.n_seq, T, H, R, Dc - R, cache.shape[1], float(scale),
-                                       int(window), _ptr(gate), gs, _stream(dev)))
+                                       int(window), _ptr(gate), gs, _ptr(ws), nws, _stream(dev)))
     return out

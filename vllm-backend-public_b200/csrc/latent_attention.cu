@@ -21,7 +21,7 @@
 
 namespace {
 
-constexpr int kMaxRPerLane = 16;                     // R <= 512 in the warp kernel
+constexpr int kMaxRPerLane = 32;                     // R <= 1024 in the warp kernel
 
 template <typename T>
 __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t proj_stride, int H, int dn, int dr, int rot_dims, int R,
@@ -170,7 +170,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
                             const int32_t* __restrict__ block_tables, int max_nb, const int32_t* __restrict__ cu_q,
                             const int32_t* __restrict__ ctx_start, int n_seq, int H, int Hc, int dr, int bs, float scale_log2,
                             int window, int stages, const __nv_bfloat16* __restrict__ gate, int64_t gate_stride,
-                            __nv_bfloat16* __restrict__ out) {
+                            __nv_bfloat16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml) {
     constexpr int R = 16 * RT;
     const int Dc = R + dr, LD = Dc + 8, vecs = Dc / 8;
     extern __shared__ __align__(16) unsigned char lat_smem[];
@@ -196,6 +196,15 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
     const int tok0 = cu_q[seq] + t0;                                        // batch row of the CTA's first token
     const int ntok = min(Gt, cu_q[seq + 1] - tok0);
     const int ctx = ctx_start[seq];
+    const int nsplit = gridDim.z, zs = blockIdx.z;                          // the CTA's share of the key tiles (decode batches)
+    if (ctx < 0 && nsplit > 1) {                                            // padding: the merge turns "no keys" into zero rows
+        for (int rr = tid; rr < ntok * nh; rr += 256) {
+            float* ml = ws_ml + (((size_t)(tok0 + rr / nh) * H + h0 + rr % nh) * nsplit + zs) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.f;
+        }
+        return;
+    }
     if (ctx < 0) {                                                          // padding: zero rows
         for (int idx = tid; idx < ntok * nh * (R / 8); idx += 256) {
             const int rr = idx / (R / 8), c = (idx % (R / 8)) * 8;
@@ -241,10 +250,11 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const bool active = wm * 16 < ntok * Hc;                                // a row group without rows only helps to copy
-    const int ntiles = (p_last - klo) / kLK + 1;
-    issue(klo, 0);
-    for (int t = 0; t < ntiles; ++t) {
-        const int kv0 = klo + t * kLK, buf = stages == 2 ? (t & 1) : 0;
+    const int all_tiles = (p_last - klo) / kLK + 1, per = (all_tiles + nsplit - 1) / nsplit;
+    const int t_begin = zs * per, ntiles = min(all_tiles, t_begin + per);
+    if (t_begin < ntiles) issue(klo + t_begin * kLK, 0);
+    for (int t = t_begin; t < ntiles; ++t) {
+        const int kv0 = klo + t * kLK, buf = stages == 2 ? ((t - t_begin) & 1) : 0;
         if (stages == 2 && t + 1 < ntiles) {                                // the next tile streams in while this one is multiplied
             issue(kv0 + kLK, buf ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -334,6 +344,20 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const int ta = ra / Hc, ha = ra % Hc, tb = rb / Hc, hb = rb % Hc;
     const bool va = ta < ntok && ha < nh, vb = tb < ntok && hb < nh;
+    if (nsplit > 1) {                                                       // partial (max, sum, unnormalised output) of this share
+        const size_t ia = ((size_t)(tok0 + ta) * H + h0 + ha) * nsplit + zs, ib = ((size_t)(tok0 + tb) * H + h0 + hb) * nsplit + zs;
+        if (wn == 0 && tq == 0) {
+            if (va) { ws_ml[ia * 2] = m0; ws_ml[ia * 2 + 1] = l0; }
+            if (vb) { ws_ml[ib * 2] = m1; ws_ml[ib * 2 + 1] = l1; }
+        }
+#pragma unroll
+        for (int n = 0; n < RT; ++n) {
+            const int col = wn * (R / 2) + n * 8 + 2 * tq;
+            if (va) *reinterpret_cast<float2*>(ws_o + ia * R + col) = make_float2(o[n][0], o[n][1]);
+            if (vb) *reinterpret_cast<float2*>(ws_o + ib * R + col) = make_float2(o[n][2], o[n][3]);
+        }
+        return;
+    }
     float f0 = l0 > 0.f ? 1.f / l0 : 0.f, f1 = l1 > 0.f ? 1.f / l1 : 0.f;
     if (gate) {
         if (va) f0 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(tok0 + ta) * gate_stride + h0 + ha]));
@@ -349,26 +373,307 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
     }
 }
 
+// ------------------------------------------------------------------------------------------------- decode rows
+// bf16, R >= 128, every sequence of the batch has ONE row: a CTA takes one token x up to 16 heads (one m16 row group), so
+// the eight warps cannot share rows -- they share the KEYS of a tile instead.  Warp w scores keys 8w .. 8w+7 of the 64-key
+// tile against all 16 rows, the row maxima meet in shared memory, every warp writes its 16 x 8 slice of P (bf16) to a
+// shared P tile, and then multiplies the whole P tile with ITS R / 8 output columns of the key rows.  No score is computed
+// twice, and the chain of dependent instructions per tile is an eighth of what one warp per row group would run.
+constexpr int kPLD = kLK + 8;
+
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+template <int RT>
+__global__ void __launch_bounds__(256)
+latent_attention_decode_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ cache,
+                               const int32_t* __restrict__ block_tables, int max_nb, const int32_t* __restrict__ cu_q,
+                               const int32_t* __restrict__ ctx_start, int H, int dr, int bs, float scale_log2, int window,
+                               const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out,
+                               float* __restrict__ ws_o, float* __restrict__ ws_ml) {
+    constexpr int R = 16 * RT, CW = R / 8, NTO = CW / 8;                    // output columns / n-tiles per warp
+    static_assert(CW % 16 == 0, "a warp owns whole pairs of n-tiles");
+    const int Dc = R + dr, LD = Dc + 8, vecs = Dc / 8;
+    extern __shared__ __align__(16) unsigned char lat_smem[];
+    __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(lat_smem);       // [16][LD]
+    __nv_bfloat16* k_sm = q_sm + 16 * LD;                                   // [2][64][LD]
+    __nv_bfloat16* p_sm = k_sm + 2 * kLK * LD;                              // [16][kPLD]
+    float* mx_sm = reinterpret_cast<float*>(p_sm + 16 * kPLD);              // [8][16]: row maxima, later row sums, per warp
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int seq = blockIdx.x, tok = cu_q[seq];
+    const int h0 = blockIdx.y * 16, nh = min(16, H - h0);
+    const int nsplit = gridDim.z, zs = blockIdx.z;
+    const int ctx = ctx_start[seq];
+    if (ctx < 0) {                                                          // padding
+        if (nsplit > 1) {
+            for (int rr = tid; rr < nh; rr += 256) {
+                float* ml = ws_ml + (((size_t)tok * H + h0 + rr) * nsplit + zs) * 2;
+                ml[0] = -INFINITY;
+                ml[1] = 0.f;
+            }
+        } else {
+            for (int idx = tid; idx < nh * (R / 8); idx += 256)
+                *reinterpret_cast<uint4*>(out + ((size_t)tok * H + h0 + idx / (R / 8)) * R + (idx % (R / 8)) * 8) = make_uint4(0, 0, 0, 0);
+        }
+        return;
+    }
+    const int pos = ctx;
+    const int klo = window > 0 ? max(pos - window + 1, 0) : 0;
+    const int32_t* bt = block_tables + (size_t)seq * max_nb;
+    for (int idx = tid; idx < 16 * vecs; idx += 256) {
+        const int r = idx / vecs, c = (idx % vecs) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nh) v = *reinterpret_cast<const uint4*>(qa + ((size_t)tok * H + h0 + r) * Dc + c);
+        *reinterpret_cast<uint4*>(q_sm + r * LD + c) = v;
+    }
+    const int gq = lane >> 2, tq = lane & 3;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[NTO][4];
+#pragma unroll
+    for (int n = 0; n < NTO; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const uint32_t q_base = b2::smem_u32(q_sm), k_base0 = b2::smem_u32(k_sm), p_base = b2::smem_u32(p_sm);
+    const int ksteps = Dc / 16;
+    const int ld_key = tid >> 2, ld_sub = (tid & 3) * 8;
+    auto issue = [&](int kv0, int buf) {
+        const int j = kv0 + ld_key;
+        __nv_bfloat16* dst = k_sm + (size_t)buf * kLK * LD + ld_key * LD;
+        if (j <= pos) {
+            const __nv_bfloat16* src = cache + ((size_t)bt[j / bs] * bs + j % bs) * Dc;
+            for (int c = ld_sub; c < Dc; c += 32) cp_async16(dst + c, src + c);
+        } else {
+            for (int c = ld_sub; c < Dc; c += 32) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int all_tiles = (pos - klo) / kLK + 1, per = (all_tiles + nsplit - 1) / nsplit;
+    const int t_begin = zs * per, ntiles = min(all_tiles, t_begin + per);
+    if (t_begin < ntiles) issue(klo + t_begin * kLK, 0);
+    for (int t = t_begin; t < ntiles; ++t) {
+        const int kv0 = klo + t * kLK, buf = (t - t_begin) & 1;
+        if (t + 1 < ntiles) {
+            issue(kv0 + kLK, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();                                                    // the tile (and, first time, Q) is in shared memory
+        const uint32_t k_base = k_base0 + (uint32_t)buf * kLK * LD * 2u;
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};                                 // 16 rows x this warp's 8 keys
+#pragma unroll 4
+        for (int kk = 0; kk < ksteps; ++kk) {
+            uint32_t a0, a1, a2, a3, b0, b1;
+            b2::ldmatrix_x4(q_base + 2u * ((lane & 15) * LD + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+            ldmatrix_x2(k_base + 2u * ((w * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1);
+            b2::mma_bf16_16816(sc, a0, a1, a2, a3, b0, b1);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = kv0 + w * 8 + 2 * tq + (e & 1);
+            sc[e] = (j >= klo && j <= pos) ? sc[e] * scale_log2 : -INFINITY;
+        }
+        float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]);
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (tq == 0) {
+            mx_sm[w * 16 + gq] = mx0;
+            mx_sm[w * 16 + gq + 8] = mx1;
+        }
+        __syncthreads();                                                    // every warp's row maxima of this tile
+        float mn0 = m0, mn1 = m1;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+            mn0 = fmaxf(mn0, mx_sm[x * 16 + gq]);
+            mn1 = fmaxf(mn1, mx_sm[x * 16 + gq + 8]);
+        }
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = exp2f(m0 - mu0), c1 = exp2f(m1 - mu1);
+        m0 = mn0;
+        m1 = mn1;
+        sc[0] = exp2f(sc[0] - mu0);
+        sc[1] = exp2f(sc[1] - mu0);
+        sc[2] = exp2f(sc[2] - mu1);
+        sc[3] = exp2f(sc[3] - mu1);
+        l0 = l0 * c0 + sc[0] + sc[1];                                       // sums over this warp's keys only
+        l1 = l1 * c1 + sc[2] + sc[3];
+        *reinterpret_cast<uint32_t*>(p_sm + gq * kPLD + w * 8 + 2 * tq) = b2::pack_bf16x2(sc[0], sc[1]);
+        *reinterpret_cast<uint32_t*>(p_sm + (gq + 8) * kPLD + w * 8 + 2 * tq) = b2::pack_bf16x2(sc[2], sc[3]);
+#pragma unroll
+        for (int n = 0; n < NTO; ++n) {
+            o[n][0] *= c0;
+            o[n][1] *= c0;
+            o[n][2] *= c1;
+            o[n][3] *= c1;
+        }
+        __syncthreads();                                                    // the P tile is complete
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            b2::ldmatrix_x4(p_base + 2u * ((lane & 15) * kPLD + ks * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+#pragma unroll
+            for (int n2 = 0; n2 < NTO / 2; ++n2) {
+                uint32_t b0, b1, b2_, b3;
+                const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = w * CW + n2 * 16 + (lane >> 4) * 8;
+                b2::ldmatrix_x4_trans(k_base + 2u * (key * LD + col), b0, b1, b2_, b3);
+                b2::mma_bf16_16816(o[2 * n2], a0, a1, a2, a3, b0, b1);
+                b2::mma_bf16_16816(o[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+            }
+        }
+        __syncthreads();                                                    // the tile, P and the maxima are consumed
+    }
+    // the row sums of the eight key slices
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (tq == 0) {
+        mx_sm[w * 16 + gq] = l0;
+        mx_sm[w * 16 + gq + 8] = l1;
+    }
+    __syncthreads();
+    l0 = l1 = 0.f;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        l0 += mx_sm[x * 16 + gq];
+        l1 += mx_sm[x * 16 + gq + 8];
+    }
+    const bool va = gq < nh, vb = gq + 8 < nh;
+    const size_t ra = (size_t)tok * H + h0 + gq, rb = ra + 8;
+    if (nsplit > 1) {
+        if (w == 0 && tq == 0) {
+            if (va) { ws_ml[(ra * nsplit + zs) * 2] = m0; ws_ml[(ra * nsplit + zs) * 2 + 1] = l0; }
+            if (vb) { ws_ml[(rb * nsplit + zs) * 2] = m1; ws_ml[(rb * nsplit + zs) * 2 + 1] = l1; }
+        }
+#pragma unroll
+        for (int n = 0; n < NTO; ++n) {
+            const int col = w * CW + n * 8 + 2 * tq;
+            if (va) *reinterpret_cast<float2*>(ws_o + (ra * nsplit + zs) * R + col) = make_float2(o[n][0], o[n][1]);
+            if (vb) *reinterpret_cast<float2*>(ws_o + (rb * nsplit + zs) * R + col) = make_float2(o[n][2], o[n][3]);
+        }
+        return;
+    }
+    float f0 = l0 > 0.f ? 1.f / l0 : 0.f, f1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (gate) {
+        if (va) f0 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)tok * gate_stride + h0 + gq]));
+        if (vb) f1 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)tok * gate_stride + h0 + gq + 8]));
+    }
+#pragma unroll
+    for (int n = 0; n < NTO; ++n) {
+        const int col = w * CW + n * 8 + 2 * tq;
+        if (va) *reinterpret_cast<uint32_t*>(out + ra * R + col) = b2::pack_bf16x2(o[n][0] * f0, o[n][1] * f0);
+        if (vb) *reinterpret_cast<uint32_t*>(out + rb * R + col) = b2::pack_bf16x2(o[n][2] * f1, o[n][3] * f1);
+    }
+}
+
+// out[row, :] = gate * sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M) over the shares of a (token, head) row
+__global__ void latent_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, int nsplit, int R, int H,
+                                    const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out) {
+    const int row = blockIdx.x;                                             // token * H + head
+    const float* ml = ws_ml + (size_t)row * nsplit * 2;
+    float M = -INFINITY;
+    for (int z = 0; z < nsplit; ++z) M = fmaxf(M, ml[2 * z]);
+    float L = 0.f;
+    if (M > -INFINITY)
+        for (int z = 0; z < nsplit; ++z) L += ml[2 * z + 1] * (ml[2 * z] == -INFINITY ? 0.f : exp2f(ml[2 * z] - M));
+    float f = L > 0.f ? 1.f / L : 0.f;
+    if (gate) f *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(row / H) * gate_stride + row % H]));
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float a = 0.f;
+        if (L > 0.f)
+            for (int z = 0; z < nsplit; ++z)
+                if (ml[2 * z] > -INFINITY) a = fmaf(ws_o[((size_t)row * nsplit + z) * R + c], exp2f(ml[2 * z] - M), a);
+        out[(size_t)row * R + c] = __float2bfloat16_rn(a * f);
+    }
+}
+
+inline int latent_sm_count() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+// Which kernel and how many shares of the key tiles per CTA row: a batch that cannot fill the GPU (decode rows) splits its
+// keys over CTAs.  decode: every sequence has one row and the latent is wide enough for eight column slices.
+struct LatentPlan {
+    bool decode;
+    int nsplit;
+};
+inline LatentPlan latent_plan(int T, int n_seq, int H, int R, int window, int max_nb, int bs) {
+    LatentPlan p;
+    p.decode = T == n_seq && R >= 128;
+    const int Hc = H < kLQ ? H : kLQ, Gt = kLQ / Hc;
+    const long ctas = p.decode ? (long)T * ((H + 15) / 16) : (long)(T < T / Gt + n_seq ? T : T / Gt + n_seq) * ((H + Hc - 1) / Hc);
+    long keys = (long)max_nb * bs;
+    const int span = p.decode ? 1 : Gt;
+    if (window > 0 && window + span < keys) keys = window + span;
+    const long tiles = (keys + kLK - 1) / kLK;
+    long n = latent_sm_count() / (ctas > 0 ? ctas : 1);
+    if (n > tiles / 2) n = tiles / 2;
+    if (n > 16) n = 16;
+    p.nsplit = n < 1 ? 1 : (int)n;
+    return p;
+}
+
 template <int RT>
 int launch_latent_mma(void* out, const void* qa, const void* cache, const int32_t* block_tables, int max_nb, const int32_t* cu_q,
                       const int32_t* ctx_start, int n_seq, int T, int H, int dr, int bs, float scale, int window, const void* gate,
-                      int64_t gate_stride, cudaStream_t st) {
+                      int64_t gate_stride, bool decode, int nsplit, float* ws, cudaStream_t st) {
     const int Dc = 16 * RT + dr, Hc = H < kLQ ? H : kLQ, Gt = kLQ / Hc;
     const size_t tile = (size_t)kLK * (Dc + 8) * sizeof(__nv_bfloat16);
     const int stages = 3 * tile <= 227 * 1024 - 64 ? 2 : 1;                 // two key tiles in flight when they fit beside Q
     const size_t smem = (size_t)(1 + stages) * tile;
     auto kern = latent_attention_mma_kernel<RT>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int tiles = T / Gt + n_seq;                       // upper bound on sum(ceil(len / Gt)); spare CTAs leave at once
-    kern<<<dim3(tiles, (H + Hc - 1) / Hc), 256, smem, st>>>(
+    const int tiles = T < T / Gt + n_seq ? T : T / Gt + n_seq;   // upper bound on sum(ceil(len / Gt)); spare CTAs leave at once
+    float* ws_o = ws;
+    float* ws_ml = ws ? ws + (size_t)T * H * nsplit * 16 * RT : nullptr;
+    if constexpr (RT >= 8) {
+        if (decode) {
+            const size_t dsm = (size_t)(16 + 2 * kLK) * (Dc + 8) * sizeof(__nv_bfloat16) + 16 * kPLD * sizeof(__nv_bfloat16) + 128 * sizeof(float);
+            auto dk = latent_attention_decode_kernel<RT>;
+            if (dsm > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(dk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm));
+            dk<<<dim3(T, (H + 15) / 16, nsplit), 256, dsm, st>>>(
+                static_cast<const __nv_bfloat16*>(qa), static_cast<const __nv_bfloat16*>(cache), block_tables, max_nb, cu_q, ctx_start,
+                H, dr, bs, scale * 1.4426950408889634f, window, static_cast<const __nv_bfloat16*>(gate), gate_stride,
+                static_cast<__nv_bfloat16*>(out), ws_o, ws_ml);
+            if (nsplit > 1)
+                latent_merge_kernel<<<T * H, 128, 0, st>>>(ws_o, ws_ml, nsplit, 16 * RT, H, static_cast<const __nv_bfloat16*>(gate),
+                                                           gate_stride, static_cast<__nv_bfloat16*>(out));
+            B2_CUDA_OK(cudaGetLastError());
+            return B2_OK;
+        }
+    }
+    kern<<<dim3(tiles, (H + Hc - 1) / Hc, nsplit), 256, smem, st>>>(
         static_cast<const __nv_bfloat16*>(qa), static_cast<const __nv_bfloat16*>(cache), block_tables, max_nb, cu_q, ctx_start,
         n_seq, H, Hc, dr, bs, scale * 1.4426950408889634f, window, stages, static_cast<const __nv_bfloat16*>(gate), gate_stride,
-        static_cast<__nv_bfloat16*>(out));
+        static_cast<__nv_bfloat16*>(out), ws_o, ws_ml);
+    if (nsplit > 1)
+        latent_merge_kernel<<<T * H, 128, 0, st>>>(ws_o, ws_ml, nsplit, 16 * RT, H, static_cast<const __nv_bfloat16*>(gate),
+                                                   gate_stride, static_cast<__nv_bfloat16*>(out));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
 
+inline bool latent_mma_ok(int act_dtype, int R, int dr, const void* qa, const void* cache, const void* out) {
+    return act_dtype == B2_ACT_BF16 && (R == 64 || R == 128 || R == 256 || R == 512) && dr % 16 == 0 && b2_aligned16(qa) &&
+           b2_aligned16(cache) && b2_aligned16(out) && (size_t)(kLQ + kLK) * (R + dr + 8) * 2 <= 227 * 1024;
+}
+
 }  // namespace
+
+// fp32 scratch (in floats) b2_latent_attention wants for this call; 0 when it needs none
+extern "C" int64_t b2_latent_attention_workspace(int act_dtype, int T, int n_seq, int H, int R, int dr, int bs, int window,
+                                                 int max_nb) {
+    if (T <= 0 || n_seq <= 0 || H <= 0 || !latent_mma_ok(act_dtype, R, dr, nullptr, nullptr, nullptr)) return 0;
+    const int n = latent_plan(T, n_seq, H, R, window, max_nb, bs).nsplit;
+    return n > 1 ? (int64_t)T * H * n * (R + 2) : 0;
+}
 
 extern "C" int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dtype, int T, int H, int dn, int dr, int rot_dims,
                               int R, int q_off, int dkv_off, const float* norm_w, float eps, const int32_t* positions,
@@ -392,17 +697,19 @@ extern "C" int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dty
 extern "C" int b2_latent_attention(void* out, const void* qa, const void* cache, int act_dtype, const int32_t* block_tables,
                                    int max_nb, const int32_t* cu_q, const int32_t* ctx_start, int n_seq, int T, int H, int R,
                                    int dr, int bs, float scale, int window, const void* gate, int64_t gate_stride,
-                                   void* stream) {
+                                   float* workspace, int64_t workspace_floats, void* stream) {
     B2_REQUIRE(T >= 0 && H > 0 && R > 0 && dr >= 0 && bs > 0 && window >= 0, B2_EINVAL, "latent_attention: bad sizes");
     B2_REQUIRE(R <= 32 * kMaxRPerLane, B2_EUNSUPPORTED, "latent_attention: latent size %d above %d", R, 32 * kMaxRPerLane);
     if (T == 0 || n_seq == 0) return B2_OK;
     B2_REQUIRE(out && qa && cache && block_tables && cu_q && ctx_start, B2_EINVAL, "latent_attention: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (act_dtype == B2_ACT_BF16 && (R == 64 || R == 128 || R == 256 || R == 512) && dr % 16 == 0 && b2_aligned16(qa) &&
-        b2_aligned16(cache) && b2_aligned16(out) && (size_t)(kLQ + kLK) * (R + dr + 8) * 2 <= 227 * 1024) {
+    if (latent_mma_ok(act_dtype, R, dr, qa, cache, out)) {
+        const LatentPlan plan = latent_plan(T, n_seq, H, R, window, max_nb, bs);
+        int nsplit = plan.nsplit;
+        if (nsplit > 1 && (!workspace || workspace_floats < (int64_t)T * H * nsplit * (R + 2))) nsplit = 1;
 #define B2_LAT(RT)                                                                                                            \
     return launch_latent_mma<RT>(out, qa, cache, block_tables, max_nb, cu_q, ctx_start, n_seq, T, H, dr, bs, scale, window, gate, \
-                                 gate_stride, st)
+                                 gate_stride, plan.decode, nsplit, nsplit > 1 ? workspace : nullptr, st)
         if (R == 64) B2_LAT(4);
         if (R == 128) B2_LAT(8);
         if (R == 256) B2_LAT(16);
