@@ -72,6 +72,64 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t proj_stri
     }
 }
 
+// The same with four elements per access (8 or 16 bytes) for row layouts whose offsets are all multiples of four.
+template <typename T>
+__global__ void latent_prep_vec_kernel(const T* __restrict__ proj, int64_t proj_stride, int H, int dn, int dr, int rot_dims, int R,
+                                       int q_off, int dkv_off, const float* __restrict__ norm_w, float eps,
+                                       const int32_t* __restrict__ positions, const float* __restrict__ cos_sin, int max_pos,
+                                       const int64_t* __restrict__ slots, T* __restrict__ qa, T* __restrict__ cache) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const T* row = proj + (size_t)t * proj_stride;
+    const int Dc = R + dr, half = rot_dims / 2;
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + (size_t)pos * rot_dims;
+    auto turn = [&](float (&v)[4], int i) {          // entries i .. i+3 of a rotated part: two pairs
+#pragma unroll
+        for (int c = 0; c < 4; c += 2) {
+            if (i + c < rot_dims) {
+                const int pr = (i + c) >> 1;
+                const float co = cs[pr], si = cs[half + pr], u = v[c], w = v[c + 1];
+                v[c] = u * co - w * si;
+                v[c + 1] = w * co + u * si;
+            }
+        }
+    };
+    for (int e = threadIdx.x * 4; e < H * dr; e += blockDim.x * 4) {
+        const int hh = e / dr, i = e % dr;
+        float v[4];
+        b2::ld4(row + q_off + (size_t)hh * (dn + dr) + dn + i, v);
+        turn(v, i);
+        b2::st4(qa + ((size_t)t * H + hh) * Dc + R + i, v);
+    }
+    if (dkv_off < 0) return;
+    const int64_t slot = slots[t];
+    if (slot < 0) return;                            // uniform over the block
+    T* dst = cache + (size_t)slot * Dc;
+    const T* src = row + dkv_off;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < R; i += blockDim.x * 4) {
+        float v[4];
+        b2::ld4(src + i, v);
+        ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    }
+    const float inv = rsqrtf(b2::block_sum(ss, red) / (float)R + eps);
+    for (int i = threadIdx.x * 4; i < R; i += blockDim.x * 4) {
+        float v[4];
+        b2::ld4(src + i, v);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[c] *= inv * (norm_w ? norm_w[i + c] : 1.f);
+        b2::st4(dst + i, v);
+    }
+    for (int i = threadIdx.x * 4; i < dr; i += blockDim.x * 4) {
+        float v[4];
+        b2::ld4(src + R + i, v);
+        turn(v, i);
+        b2::st4(dst + R + i, v);
+    }
+}
+
 // One warp per (row, head): scores of 32 keys at a time (a lane per key), online softmax, P.C with a lane per latent column.
 // Any sizes, both activation types; the tensor-core kernel below takes the bf16 shapes it is built for.
 template <typename T>
@@ -686,10 +744,19 @@ extern "C" int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dty
     B2_REQUIRE(dkv_off < 0 || (slots && cache), B2_EINVAL, "latent_prep: a layer with a down-projection needs slots and its pool");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int work = H * dr > R ? H * dr : R;
-    const int threads = work >= 512 ? 256 : 128;
-    B2_DISPATCH_ACT(act_dtype, A, (latent_prep_kernel<A><<<T, threads, 0, st>>>(
-        static_cast<const A*>(proj), proj_stride, H, dn, dr, rot_dims, R, q_off, dkv_off, norm_w, eps, positions, cos_sin, max_pos,
-        slots, bs, static_cast<A*>(qa), static_cast<A*>(cache))));
+    const int threads = work >= 2048 ? 256 : 128;
+    const bool vec = proj_stride % 4 == 0 && q_off % 4 == 0 && dn % 4 == 0 && dr % 4 == 0 && R % 4 == 0 && rot_dims % 4 == 0 &&
+                     (dkv_off < 0 || dkv_off % 4 == 0) && b2_aligned16(proj) && b2_aligned16(qa) && (dkv_off < 0 || b2_aligned16(cache));
+    B2_DISPATCH_ACT(act_dtype, A, {
+        if (vec)
+            latent_prep_vec_kernel<A><<<T, threads, 0, st>>>(static_cast<const A*>(proj), proj_stride, H, dn, dr, rot_dims, R, q_off,
+                                                             dkv_off, norm_w, eps, positions, cos_sin, max_pos, slots,
+                                                             static_cast<A*>(qa), static_cast<A*>(cache));
+        else
+            latent_prep_kernel<A><<<T, threads, 0, st>>>(static_cast<const A*>(proj), proj_stride, H, dn, dr, rot_dims, R, q_off,
+                                                         dkv_off, norm_w, eps, positions, cos_sin, max_pos, slots, bs,
+                                                         static_cast<A*>(qa), static_cast<A*>(cache));
+    });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }

@@ -17,23 +17,6 @@
 
 namespace {
 
-// four consecutive elements of an activation row (8 or 16 bytes, aligned)
-__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
-    const float4 t = *reinterpret_cast<const float4*>(p);
-    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-}
-__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&v)[4]) {
-    const uint2 t = *reinterpret_cast<const uint2*>(p);
-    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
-    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
-}
-__device__ __forceinline__ void st4(float* p, const float (&v)[4]) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
-    *reinterpret_cast<uint2*>(p) = make_uint2(b2::pack_bf16x2(v[0], v[1]), b2::pack_bf16x2(v[2], v[3]));
-}
-
 // W = 4: every access is a 16-byte (fp32) or 8-byte (bf16) vector; W = 1: any width and alignment.  A thread keeps to its
 // own columns in every pass, so the row in shared memory needs no barrier beyond those of the reductions.
 template <typename T, int W>
@@ -51,7 +34,7 @@ sandwich_norm_kernel(float* __restrict__ x, int D, const T* __restrict__ y, int6
         const T* yt = y + (size_t)t * y_stride;
         for (int d = threadIdx.x * W; d < D; d += step) {
             float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (W == 4) ld4(yt + d, v); else v[0] = b2::ld(yt + d);
+            if (W == 4) b2::ld4(yt + d, v); else v[0] = b2::ld(yt + d);
 #pragma unroll
             for (int c = 0; c < W; ++c) {
                 row_sm[d + c] = v[c];
@@ -74,7 +57,7 @@ sandwich_norm_kernel(float* __restrict__ x, int D, const T* __restrict__ y, int6
         sum = 0.f;
         for (int d = threadIdx.x * W; d < D; d += step) {
             float r[4] = {0.f, 0.f, 0.f, 0.f};
-            if (W == 4) ld4(xt + d, r); else r[0] = xt[d];
+            if (W == 4) b2::ld4(xt + d, r); else r[0] = xt[d];
 #pragma unroll
             for (int c = 0; c < W; ++c) {
                 float v = row_sm[d + c];
@@ -83,12 +66,12 @@ sandwich_norm_kernel(float* __restrict__ x, int D, const T* __restrict__ y, int6
                 row_sm[d + c] = r[c];
                 sum += r[c];
             }
-            if (W == 4) st4(xt + d, r); else xt[d] = r[0];
+            if (W == 4) b2::st4(xt + d, r); else xt[d] = r[0];
         }
     } else {
         for (int d = threadIdx.x * W; d < D; d += step) {
             float r[4] = {0.f, 0.f, 0.f, 0.f};
-            if (W == 4) ld4(xt + d, r); else r[0] = xt[d];
+            if (W == 4) b2::ld4(xt + d, r); else r[0] = xt[d];
 #pragma unroll
             for (int c = 0; c < W; ++c) {
                 row_sm[d + c] = r[c];
@@ -113,7 +96,7 @@ sandwich_norm_kernel(float* __restrict__ x, int D, const T* __restrict__ y, int6
         float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < W; ++c) v[c] = (row_sm[d + c] - mean) * inv * pre_w[d + c] + (pre_b ? pre_b[d + c] : 0.f);
-        if (W == 4) st4(ho + d, v); else b2::st(ho + d, v[0]);
+        if (W == 4) b2::st4(ho + d, v); else b2::st(ho + d, v[0]);
     }
 }
 
@@ -122,13 +105,13 @@ __global__ void relu_sq_kernel(T* __restrict__ out, int64_t out_stride, const T*
     const int t = blockIdx.x;
     for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * W; i < I; i += gridDim.y * blockDim.x * W) {
         float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (W == 4) ld4(in + (size_t)t * in_stride + i, v); else v[0] = b2::ld(in + (size_t)t * in_stride + i);
+        if (W == 4) b2::ld4(in + (size_t)t * in_stride + i, v); else v[0] = b2::ld(in + (size_t)t * in_stride + i);
 #pragma unroll
         for (int c = 0; c < W; ++c) {
             v[c] = fmaxf(v[c], 0.f);
             v[c] *= v[c];
         }
-        if (W == 4) st4(out + (size_t)t * out_stride + i, v); else b2::st(out + (size_t)t * out_stride + i, v[0]);
+        if (W == 4) b2::st4(out + (size_t)t * out_stride + i, v); else b2::st(out + (size_t)t * out_stride + i, v[0]);
     }
 }
 
