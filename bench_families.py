@@ -203,7 +203,7 @@ def _kernels_gatolix(size, s, B, ctx, T):
         _emit(bench="kernel", size=size, kernel=kernel, phase=phase, ms=round(ms, 4), gb_per_s=round(gbs, 1),
               tflop_per_s=round(tfs, 2), frac_hbm=round(gbs / HBM, 3), frac_bf16=round(tfs / TF, 4), peaks=src, like=like)
 
-    tab = ops.rotary_table(ctx + T + 64, dr, 500000.0, {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}, dev)
+    tab = ops.rotary_table(ctx + T + 64, dr, 10000.0, {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}, dev)
     for phase, n_seq, q_len, c in (("prefill", 1, T, 0), ("decode", B, 1, ctx)):
         rows = n_seq * q_len
         nb_seq = (c + q_len + 15) // 16

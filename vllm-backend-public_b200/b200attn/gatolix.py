@@ -177,10 +177,10 @@ def bench_config(hidden: int, layers: int, heads: int, dim: int, rot_dim: int, v
     """A model-sized geometry for benchmarks: layer 0 dense, the rest routed; every `share_every`-th layer owns a latent
     pool and the layers after it read it."""
     specs = []
-    scaling = {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    scaling = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
     for i in range(layers):
         owner = i - i % max(share_every, 1)
-        m = LatentSpec(heads, dim, rot_dim, vdim, kv_rank, (dim + rot_dim) ** -0.5, window, rot_dim, 500000.0, scaling,
+        m = LatentSpec(heads, dim, rot_dim, vdim, kv_rank, (dim + rot_dim) ** -0.5, window, rot_dim, 10000.0, scaling,
                        None if owner == i else owner)
         specs.append(LayerSpec(m, DenseSpec(ff * top) if i == 0 else ExpertsSpec(experts, top, ff, 7.0)))
     return GatolixConfig(name, vocab, hidden, specs, logit_softcap=30.0)
