@@ -24,7 +24,7 @@ def _close(got, want, dt, what=""):
 
 
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("D", [50, 200, 1000, 4096])
+@pytest.mark.parametrize("D", [50, 200, 1000, 4096, 8192])
 def test_sandwich_norm(cuda, dt, D):
     from b200attn import ops
     g = torch.Generator().manual_seed(D)
