@@ -72,7 +72,14 @@ def cfg_d():      # a window longer than any test sequence, no feed-forward in t
                            layer(mixer(5, 4, 2, 6, 8, window=3))], softcap=50.0)
 
 
-CONFIGS = {"a": cfg_a, "b": cfg_b, "c": cfg_c, "d": cfg_d}
+def cfg_e():      # nothing is a multiple of four: width 30, odd value size, latent 22, six rotated entries, expert width 10
+    return config(30, 77, [
+        layer(mixer(3, 6, 6, 5, 22, window=11, scaling={"factor": 5.0, "original": 24, "fast": 3.0, "slow": 0.25}), moe(3, 2, 10, 0.75)),
+        layer(mixer(2, 10, 6, 7, 22, window=5, scaling={"factor": 5.0, "original": 24, "fast": 3.0, "slow": 0.25}, kv_from=0), dense(21)),
+        layer(mixer(1, 2, 2, 3, 6, base=3.0))], eps=1e-4, softcap=8.0)
+
+
+CONFIGS = {"a": cfg_a, "b": cfg_b, "c": cfg_c, "d": cfg_d, "e": cfg_e}
 
 
 def oracle_logits(cfg: dict, weights, toks):

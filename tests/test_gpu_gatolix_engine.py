@@ -69,7 +69,7 @@ def test_portions_of_many_sizes(cuda, models, name, dtype):
 
 
 @pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("c", "float32"), ("d", "float32"),
-                                        ("a", "bfloat16"), ("c", "bfloat16")])
+                                        ("e", "float32"), ("a", "bfloat16"), ("c", "bfloat16"), ("e", "bfloat16")])
 def test_unequal_batches_with_reuse_of_pages(cuda, models, name, dtype):
     """Up to four live requests, prompt portions beside single tokens; requests leave and new ones take over their pages
     (a pool of 15 pages for ~320 tokens in total).  Every request equals the oracle over its own tokens, and equals
@@ -177,6 +177,60 @@ def test_random_init_and_checkpoint_shape_check(cuda, tmp_path, models):
     U.save_checkpoint(tmp_path / "lacking", cfg, lacking)
     with pytest.raises(ValueError, match="lacks"):
         U.make_engine(tmp_path / "lacking", "bfloat16")
+
+
+def test_server_serves_a_model_directory(cuda, models):
+    """`python -m b200attn.server --model DIR --dtype float32`: the family comes from config.json, a completion is the
+    oracle's greedy continuation of a token-id prompt."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    import time
+    from pathlib import Path
+
+    import requests
+    cfg, W, path = models["a"]
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root / "vllm-backend-public_b200"))
+    proc = subprocess.Popen([sys.executable, "-m", "b200attn.server", "--model", str(path), "--dtype", "float32", "--port", str(port),
+                             "--host", "127.0.0.1", "--max-num-seqs", "4", "--max-model-len", "256",
+                             "--num-gpu-blocks-override", "80", "--served-model-name", "gatolix-test"], env=env,
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        for _ in range(600):
+            if proc.poll() is not None:
+                raise RuntimeError("server exited: " + proc.stdout.read().decode()[-2000:])
+            try:
+                if requests.get(base + "/health", timeout=1).status_code == 200:
+                    break
+            except requests.RequestException:
+                pass
+            time.sleep(0.2)
+        else:
+            raise RuntimeError("server did not become healthy")
+        prompt = U.tokens(13, cfg["vocab"], 78)
+        r = requests.post(base + "/v1/completions", json={"model": "gatolix-test", "prompt": prompt, "max_tokens": 6,
+                                                          "temperature": 0.0, "ignore_eos": True}, timeout=60)
+        assert r.status_code == 200, r.text
+        body = r.json()
+        assert body["usage"]["prompt_tokens"] == 13 and body["usage"]["completion_tokens"] == 6
+        seq = list(prompt)
+        for _ in range(6):
+            seq.append(int(U.oracle_logits(cfg, W, seq)[-1].argmax()))
+        want = bytes(t % 256 for t in seq[13:]).decode("utf-8", errors="replace")      # the byte tokenizer's text
+        assert body["choices"][0]["text"] == want
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(20)
+        except subprocess.TimeoutExpired:
+            proc.kill()
 
 
 def test_trace_runner_replays_a_schedule(cuda, tmp_path, models):
