@@ -17,6 +17,9 @@
 //                         (gate NULL: 1).  Softmax state, scores and the accumulator are fp32.
 // Sequences are described like everywhere in this library: rows cu_q[i] .. cu_q[i+1]-1, ctx_start[i] cached tokens before
 // them (< 0: padding, output rows are zeroed), block_tables[i, :].
+// Every sequence of a batch has at least one row; a batch with as many rows as sequences is therefore one row each (a
+// decode step) and may take the decode kernel.  b2_latent_attention_workspace tells how much fp32 scratch a call can use
+// to split the keys of a row over CTAs; without it the call runs unsplit.
 #include "b2_act.cuh"
 
 namespace {
@@ -321,7 +324,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
         }
         __syncthreads();                                                    // the tile (and, first time, Q) is in shared memory
         const uint32_t k_base = k_base0 + (uint32_t)buf * kLK * LD * 2u;
-        if (active && !(kv0 > w_last || kv0 + kLK - 1 < w_lo)) {            // else nothing in this tile is visible to the warp's rows
+        if (active && !(kv0 > w_last || kv0 + kLK - 1 < w_lo)) {            // else no key of the tile is visible to the warp's rows
             float sc[8][4];
 #pragma unroll
             for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
@@ -380,7 +383,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfl
             }
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-                const uint32_t a0 = b2::pack_bf16x2(sc[2 * ks][0], sc[2 * ks][1]), a1 = b2::pack_bf16x2(sc[2 * ks][2], sc[2 * ks][3]);
+                const uint32_t a0 = b2::pack_bf16x2(sc[2 * ks][0], sc[2 * ks][1]),
+                               a1 = b2::pack_bf16x2(sc[2 * ks][2], sc[2 * ks][3]);
                 const uint32_t a2 = b2::pack_bf16x2(sc[2 * ks + 1][0], sc[2 * ks + 1][1]),
                                a3 = b2::pack_bf16x2(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
 #pragma unroll
@@ -472,7 +476,8 @@ latent_attention_decode_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_
             }
         } else {
             for (int idx = tid; idx < nh * (R / 8); idx += 256)
-                *reinterpret_cast<uint4*>(out + ((size_t)tok * H + h0 + idx / (R / 8)) * R + (idx % (R / 8)) * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(out + ((size_t)tok * H + h0 + idx / (R / 8)) * R + (idx % (R / 8)) * 8) =
+                    make_uint4(0, 0, 0, 0);
         }
         return;
     }
@@ -650,7 +655,8 @@ inline int latent_sm_count() {
     static int sms = 0;
     if (!sms) {
         int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             sms = 148;
     }
     return sms;
@@ -693,7 +699,8 @@ int launch_latent_mma(void* out, const void* qa, const void* cache, const int32_
     float* ws_ml = ws ? ws + (size_t)T * H * nsplit * 16 * RT : nullptr;
     if constexpr (RT >= 8) {
         if (decode) {
-            const size_t dsm = (size_t)(16 + 2 * kLK) * (Dc + 8) * sizeof(__nv_bfloat16) + 16 * kPLD * sizeof(__nv_bfloat16) + 128 * sizeof(float);
+            const size_t dsm = (size_t)(16 + 2 * kLK) * (Dc + 8) * sizeof(__nv_bfloat16) + 16 * kPLD * sizeof(__nv_bfloat16) +
+                               128 * sizeof(float);
             auto dk = latent_attention_decode_kernel<RT>;
             if (dsm > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(dk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm));
             dk<<<dim3(T, (H + 15) / 16, nsplit), 256, dsm, st>>>(
@@ -746,7 +753,8 @@ extern "C" int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dty
     const int work = H * dr > R ? H * dr : R;
     const int threads = work >= 2048 ? 256 : 128;
     const bool vec = proj_stride % 4 == 0 && q_off % 4 == 0 && dn % 4 == 0 && dr % 4 == 0 && R % 4 == 0 && rot_dims % 4 == 0 &&
-                     (dkv_off < 0 || dkv_off % 4 == 0) && b2_aligned16(proj) && b2_aligned16(qa) && (dkv_off < 0 || b2_aligned16(cache));
+                     (dkv_off < 0 || dkv_off % 4 == 0) && b2_aligned16(proj) && b2_aligned16(qa) &&
+                     (dkv_off < 0 || b2_aligned16(cache));
     B2_DISPATCH_ACT(act_dtype, A, {
         if (vec)
             latent_prep_vec_kernel<A><<<T, threads, 0, st>>>(static_cast<const A*>(proj), proj_stride, H, dn, dr, rot_dims, R, q_off,

@@ -182,8 +182,10 @@ extern "C" int b2_relu_sq(void* out, int64_t out_stride, const void* in, int64_t
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool vec = I % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && b2_aligned16(in) && b2_aligned16(out);
     B2_DISPATCH_ACT(act_dtype, A, {
-        if (vec) relu_sq_kernel<A, 4><<<rows_grid(I / 4, T), 256, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(in), in_stride, I);
-        else relu_sq_kernel<A, 1><<<rows_grid(I, T), 256, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(in), in_stride, I);
+        A* o = static_cast<A*>(out);
+        const A* i = static_cast<const A*>(in);
+        if (vec) relu_sq_kernel<A, 4><<<rows_grid(I / 4, T), 256, 0, st>>>(o, out_stride, i, in_stride, I);
+        else relu_sq_kernel<A, 1><<<rows_grid(I, T), 256, 0, st>>>(o, out_stride, i, in_stride, I);
     });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
