@@ -79,7 +79,8 @@ def latent_kv(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float):
 
 def windowed_attention(q, k, v, scale: float, window: int, first_pos: int = 0):
     """q [Tq, H, dk] at positions first_pos .. first_pos + Tq - 1; k [Tk, H, dk], v [Tk, H, dv] at positions 0 .. Tk - 1.
-    Position i sees j with 0 <= i - j < window (window 0: every j <= i).  Ordinary softmax.  Returns [Tq, H, dv]."""
+    A query at position i attends to keys max(0, i - window + 1) .. i (window 0: keys 0 .. i), plain softmax over them.
+    Returns [Tq, H, dv]."""
     Tq, H, _ = q.shape
     out = torch.zeros(Tq, H, v.shape[2], dtype=q.dtype)
     for t in range(Tq):

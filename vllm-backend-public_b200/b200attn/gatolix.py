@@ -40,7 +40,7 @@ class LatentSpec:
     vdim: int                  # per-head value size
     kv_rank: int               # latent size
     scale: float               # score scale
-    window: int = 0            # position i sees j with 0 <= i - j < window (0: plain causal)
+    window: int = 0            # a query attends to its own position and the window - 1 before it (0: plain causal)
     rot_dims: int = 0          # how many entries of the rotated part turn (the rest pass)
     rot_base: float = 10000.0
     rot_scaling: Optional[dict] = None     # {factor, original, fast, slow}
