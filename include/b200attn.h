@@ -508,6 +508,8 @@ B2_API int b2_moe_capacity(int n, int E);
 #define B2_GLU_CLAMPED 1          /* g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(alpha g') * (u' + 1) */
 B2_API int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
                         int D, int E, int top, int scoring, int32_t* ids, float* weights, void* stream);
+B2_API int b2_moe_select(const float* logits, int64_t stride, const float* bias, int T, int E, int top, int scoring,
+                         int32_t* ids, float* weights, void* stream);
 B2_API int b2_moe_align(const int32_t* ids, int n, int E, int cap, int32_t* sorted, int32_t* tile_expert, int32_t* place,
                         int32_t* group_ends /* [E] or NULL */, void* stream);
 B2_API int b2_moe_gather(const void* h, int64_t h_stride, int act_dtype, const int32_t* sorted, int cap, int top, int D,

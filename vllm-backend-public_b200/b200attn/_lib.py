@@ -117,6 +117,7 @@ SIGNATURES = {
     "b2_moe_tile_rows": (i32, []),
     "b2_moe_capacity": (i32, [i32, i32]),
     "b2_moe_route": (i32, [vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp]),
+    "b2_moe_select": (i32, [vp, i64, vp, i32, i32, i32, i32, vp, vp, vp]),
     "b2_moe_align": (i32, [vp, i32, i32, i32, vp, vp, vp, vp, vp]),
     "b2_moe_gather": (i32, [vp, i64, i32, vp, i32, i32, i32, vp, vp]),
     "b2_moe_combine": (i32, [vp, i32, vp, vp, i32, i32, i32, vp, i64, i32, vp]),

@@ -858,10 +858,19 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
     _f32(bias, "bias", (E,))
     ids = torch.empty(T, top, dtype=torch.int32, device=dev)
     wts = torch.empty(T, top, dtype=torch.float32, device=dev)
+    if T >= MOE_ROUTE_GEMM_MIN_ROWS and E * 4 * 4 <= 48 * 1024:
+        # the logits are a GEMM (bf16 operands, fp32 accumulation and fp32 result; fp32 as it is)
+        z = torch.mm(h, w_router.t(), out_dtype=torch.float32) if h.dtype == torch.bfloat16 else torch.mm(h, w_router.t())
+        _lib.check(lib.b2_moe_select(_ptr(z), E, _ptr(bias), T, E, top, int(scoring), _ptr(ids), _ptr(wts), _stream(dev)))
+        return ids, wts
     _lib.check(lib.b2_moe_route(_ptr(h), hs, _ptr(w_router), _ptr(bias), _act(h, "h"), T, D, E, top, int(scoring), _ptr(ids),
                                 _ptr(wts), _stream(dev)))
     return ids, wts
 
+
+# From this many rows on the router logits of a batch are one library GEMM followed by b2_moe_select; smaller batches (a few decode
+# rows) compute logits and choice in one launch of b2_moe_route, which re-reads the router matrix per token.
+MOE_ROUTE_GEMM_MIN_ROWS = 16
 
 # Above this many (token, choice) pairs the two expert products of a bf16 batch are compute bound and go to the vendor's
 # grouped GEMM (torch._grouped_mm over the expert-sorted rows, group offsets read on the device); below it they stream the

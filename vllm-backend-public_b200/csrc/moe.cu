@@ -3,6 +3,7 @@
 //   b2_moe_route     z = W_r h in fp32 (one warp per token).  B2_ROUTE_TOPK_SOFTMAX: the `top` largest of z + b (lowest index
 //                    wins a tie), weights = softmax over the chosen logits only.  B2_ROUTE_SOFTMAX_ALL: s = softmax(z) over
 //                    all experts, the `top` largest of s + b are chosen, weights = their s (not renormalised).
+//   b2_moe_select    the same choice from fp32 logits computed elsewhere (a library GEMM over a prompt batch).
 //   b2_moe_align     counting sort of the T*top (token, choice) pairs by expert into row tiles of kMoeBM rows: every tile
 //                    belongs to one expert, experts are padded to a tile boundary with -1.  Entirely on the device (no host
 //                    read of the counts), so the step stays capturable in a CUDA graph and never waits for the GPU.
@@ -24,6 +25,69 @@ namespace {
 constexpr int kMoeBM = 32, kMoeBN = 64, kMoeBK = 32;
 
 // ------------------------------------------------------------------------------------------------- router
+// One warp picks the `top` experts of token t from its fp32 logits z [E] in shared memory (overwritten).
+__device__ __forceinline__ void route_select(float* z, int t, int E, int top, int scoring, const float* __restrict__ bias,
+                                             int lane, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    if (scoring == B2_ROUTE_SOFTMAX_ALL) {
+        // scores over all experts; the choice adds the correction, the weight is the plain score
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = b2::warp_max(mx);
+        float den = 0.f;
+        for (int e = lane; e < E; e += 32) den += expf(z[e] - mx);
+        den = b2::warp_sum(den);
+        for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / den;
+        __syncwarp();
+        for (int j = 0; j < top; ++j) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float c = z[e] + (bias ? bias[e] : 0.f);          // a chosen expert holds -inf
+                if (c > best) { best = c; arg = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (arg == 0x7fffffff) arg = 0;
+            if (lane == 0) {
+                ids[(size_t)t * top + j] = arg;
+                wts[(size_t)t * top + j] = z[arg] == -INFINITY ? 0.f : z[arg];
+                z[arg] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        return;
+    }
+    float v0 = 0.f, sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (z[e] > best) { best = z[e]; arg = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = 0;          // every logit is NaN or -inf: still a valid expert id
+        if (j == 0) v0 = best;
+        const float p = expf(best - v0);
+        sum += p;
+        if (lane == 0) {
+            ids[(size_t)t * top + j] = arg;
+            wts[(size_t)t * top + j] = p;
+            z[arg] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    const float inv = 1.f / sum;
+    for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= inv;
+}
+
 // One CTA per TOK tokens: their rows are staged once as fp32, the warps share the experts (each logit is one warp's dot
 // product with independent partial sums per lane; a weight vector is loaded once and applied to all TOK rows, which
 // divides the L2 traffic of a prompt batch by TOK), then warp t picks the `top` largest of token t.
@@ -91,68 +155,21 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, cons
         }
     }
     __syncthreads();
-    for (int tt = wid; tt < nt; tt += nw) {
-        float* z = zs + (size_t)tt * E;
-        const int t = t0 + tt;
-        if (scoring == B2_ROUTE_SOFTMAX_ALL) {
-            // scores over all experts; the choice adds the correction, the weight is the plain score
-            float mx = -INFINITY;
-            for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-            mx = b2::warp_max(mx);
-            float den = 0.f;
-            for (int e = lane; e < E; e += 32) den += expf(z[e] - mx);
-            den = b2::warp_sum(den);
-            for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / den;
-            __syncwarp();
-            for (int j = 0; j < top; ++j) {
-                float best = -INFINITY;
-                int arg = 0x7fffffff;
-                for (int e = lane; e < E; e += 32) {
-                    const float c = z[e] + (bias ? bias[e] : 0.f);          // a chosen expert holds -inf
-                    if (c > best) { best = c; arg = e; }
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                    const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-                    if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
-                }
-                if (arg == 0x7fffffff) arg = 0;
-                if (lane == 0) {
-                    ids[(size_t)t * top + j] = arg;
-                    wts[(size_t)t * top + j] = z[arg] == -INFINITY ? 0.f : z[arg];
-                    z[arg] = -INFINITY;
-                }
-                __syncwarp();
-            }
-            continue;
-        }
-        float v0 = 0.f, sum = 0.f;
-        for (int j = 0; j < top; ++j) {
-            float best = -INFINITY;
-            int arg = 0x7fffffff;
-            for (int e = lane; e < E; e += 32)
-                if (z[e] > best) { best = z[e]; arg = e; }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
-            }
-            if (arg == 0x7fffffff) arg = 0;          // every logit is NaN or -inf: still a valid expert id
-            if (j == 0) v0 = best;
-            const float p = expf(best - v0);
-            sum += p;
-            if (lane == 0) {
-                ids[(size_t)t * top + j] = arg;
-                wts[(size_t)t * top + j] = p;
-                z[arg] = -INFINITY;
-            }
-            __syncwarp();
-        }
-        const float inv = 1.f / sum;
-        for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= inv;
-    }
+    for (int tt = wid; tt < nt; tt += nw) route_select(zs + (size_t)tt * E, t0 + tt, E, top, scoring, bias, lane, ids, wts);
+}
+
+// The same choice from logits that a library GEMM has produced (prompt batches): a warp per token.
+__global__ void moe_select_kernel(const float* __restrict__ logits, int64_t stride, const float* __restrict__ bias, int rows, int E,
+                                  int top, int scoring, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float route_sm[];              // z [warps][E]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + wid;
+    if (t >= rows) return;
+    float* z = route_sm + (size_t)wid * E;
+    for (int e = lane; e < E; e += 32)
+        z[e] = logits[(size_t)t * stride + e] + ((bias && scoring == B2_ROUTE_TOPK_SOFTMAX) ? bias[e] : 0.f);
+    __syncwarp();
+    route_select(z, t, E, top, scoring, bias, lane, ids, wts);
 }
 
 // ------------------------------------------------------------------------------------------------- align
@@ -492,6 +509,22 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
                                               scoring, vec, vec16, ids, weights);
         }
     });
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_moe_select(const float* logits, int64_t stride, const float* bias, int T, int E, int top, int scoring,
+                             int32_t* ids, float* weights, void* stream) {
+    B2_REQUIRE(T >= 0 && E > 0 && top >= 1 && top <= E && stride >= E, B2_EINVAL, "moe_select: bad sizes E=%d top=%d", E, top);
+    B2_REQUIRE(scoring == B2_ROUTE_TOPK_SOFTMAX || scoring == B2_ROUTE_SOFTMAX_ALL, B2_EINVAL, "moe_select: unknown scoring %d",
+               scoring);
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(logits && ids && weights, B2_EINVAL, "moe_select: null pointer");
+    const int warps = 4;
+    const size_t smem = (size_t)warps * E * sizeof(float);
+    B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "moe_select: %d experts do not fit shared memory", E);
+    moe_select_kernel<<<(T + warps - 1) / warps, warps * 32, smem, static_cast<cudaStream_t>(stream)>>>(logits, stride, bias, T, E, top,
+                                                                                                     scoring, ids, weights);
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
