@@ -539,6 +539,15 @@ B2_API int b2_latent_attention(void* out, const void* qa, const void* cache, int
                                int max_nb, const int32_t* cu_q, const int32_t* ctx_start, int n_seq, int T, int H, int R,
                                int dr, int bs, float scale, int window /* 0: causal */, const void* gate /* or NULL */,
                                int64_t gate_stride, float* workspace /* or NULL */, int64_t workspace_floats, void* stream);
+/* long prompt portions: the latent rows a portion can see, gathered to one buffer; attention over per-head keys and values
+ * rebuilt from it (key = [kn[g, h, :dn] | kt[g, :dr]], query = [qn[t, h, :dn] | qr[t, h, :dr]]), sliding window, gate */
+B2_API int b2_latent_gather(void* out, const void* cache, const int32_t* block_tables, int max_nb, const int32_t* cu_k,
+                            const int32_t* k_lo, int n_seq, int N, int bs, int Dc, void* stream);
+B2_API int b2_window_attention(void* out, const void* qn, int64_t qn_row, int qn_head, const void* qr, int64_t qr_row,
+                               int qr_head, const void* kn, const void* kt, int64_t kt_row, const void* v,
+                               const int32_t* cu_q, const int32_t* ctx_start, const int32_t* cu_k, const int32_t* k_lo,
+                               int n_seq, int T, int H, int dn, int dr, int dv, float scale, int window, const void* gate,
+                               int64_t gate_stride, void* stream);
 B2_API int64_t b2_latent_attention_workspace(int act_dtype, int T, int n_seq, int H, int R, int dr, int bs, int window,
                                              int max_nb);
 

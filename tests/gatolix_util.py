@@ -79,6 +79,16 @@ def cfg_e():      # nothing is a multiple of four: width 30, odd value size, lat
         layer(mixer(1, 2, 2, 3, 6, base=3.0))], eps=1e-4, softcap=8.0)
 
 
+def cfg_f():      # head sizes for which long prompt portions rebuild keys and values per head (bf16): a pool read with and
+    # without a window, a latent that only the warp kernel takes for the short rows beside it
+    y = {"factor": 4.0, "original": 48, "fast": 6.0, "slow": 1.5}
+    return config(64, 120, [
+        layer(mixer(4, 16, 16, 32, 64, window=100, scaling=y), dense(48)),
+        layer(mixer(2, 48, 16, 16, 64, scaling=y, kv_from=0), moe(4, 2, 32, 1.25)),
+        layer(mixer(3, 8, 24, 48, 40, window=37, base=200.0), moe(3, 1, 24, 2.5)),
+        layer(mixer(5, 40, 24, 16, 40, window=64, base=200.0, kv_from=2), dense(40))], softcap=12.0)
+
+
 CONFIGS = {"a": cfg_a, "b": cfg_b, "c": cfg_c, "d": cfg_d, "e": cfg_e}
 
 

@@ -94,6 +94,35 @@ def test_unequal_batches_with_reuse_of_pages(cuda, models, name, dtype):
     eng.close()
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_long_portions_rebuild_keys_per_head(cuda, tmp_path, monkeypatch, dtype):
+    """Steps with 256 prompt rows and more take another attention path in bf16 (keys and values per head over gathered pool
+    rows): a whole prompt, long portions with context before them (inside and beyond the windows), a long portion beside
+    decode rows and a short one, and the same requests cut small -- all against the oracle."""
+    cfg = U.cfg_f()
+    W = R.random_weights(cfg, seed=17)
+    path = U.save_checkpoint(tmp_path / "f", cfg, W)
+    V = cfg["vocab"]
+    reqs = {"p": U.tokens(620, V, 1), "q": U.tokens(300, V, 2), "r": U.tokens(40, V, 3)}
+    sched = [[("p", 300), ("r", 3)],                       # whole start of p beside a short portion
+             [("p", 1), ("r", 1), ("q", 280)],             # decode rows beside a long portion from position 0
+             [("p", 299), ("r", 1), ("q", 1)],             # a long portion with 301 tokens before it
+             [("q", 19), ("p", 20), ("r", 35)]]            # short portions again
+    from b200attn import ops
+    calls, real = [], ops.window_attention
+    monkeypatch.setattr(ops, "window_attention", lambda *a, **k: (calls.append(a[0].shape[0]), real(*a, **k))[1])
+    eng = U.make_engine(path, dtype, max_tokens=1024)
+    got = U.replay(eng, reqs, sched)
+    for rid, toks in reqs.items():
+        err = U.rel_err(got[rid], U.oracle_logits(cfg, W, toks), dtype)
+        assert err <= U.TOL[dtype], f"request {rid}: error {err:.3e} ({dtype})"
+    layers = len(cfg["layers"])
+    assert calls == ([303] * layers + [280] * layers + [299] * layers if dtype == "bfloat16" else [])
+    small = U.replay(eng, {"q": reqs["q"]}, [[("q", 100)], [("q", 100)], [("q", 100)]])
+    assert U.rel_err(small["q"], got["q"], dtype) <= U.TOL[dtype]
+    eng.close()
+
+
 @pytest.mark.parametrize("eager", [False, True])
 def test_long_decoding_through_graph_and_eager_steps(cuda, models, eager):
     """A 20-token prompt then 230 single-token steps (the decode-only step is a CUDA graph unless eager), beside a second

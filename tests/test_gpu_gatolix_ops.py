@@ -238,6 +238,56 @@ def test_latent_attention_far_key_and_padding(cuda, dt):
     _close(out[2], pool[0, 0, :16].double().cpu().expand(2, 16), dt, "a first token sees itself")
 
 
+@pytest.mark.parametrize("H,dn,dr,dv", [(3, 16, 16, 32), (2, 24, 8, 16), (5, 8, 24, 48), (4, 128, 64, 128), (1, 8, 8, 80)])
+@pytest.mark.parametrize("window", [0, 1, 40, 64, 150])
+def test_gather_and_window_attention(cuda, H, dn, dr, dv, window):
+    """Prompt portions over keys and values held per head: pool rows gathered from shuffled pages (from each window's first
+    position on, or from further back), keys = per-head part + shared part, a loud key on the window's edge."""
+    from b200attn import ops
+    g = torch.Generator().manual_seed(H * 7 + window)
+    bf, Rk, bs, scale = torch.bfloat16, 24, 16, 0.25
+    seqs = [(0, 130), (70, 65), (201, 3), (0, 1), (33, 64)]                  # (context, rows)
+    pools, tables, wants, qs, gates, kns, vs = [], [], [], [], [], [], []
+    cu_q, ctx, cu_k, k_lo = [0], [], [0], []
+    for si, (nctx, nq) in enumerate(seqs):
+        Tk = nctx + nq
+        lat = torch.randn(Tk, Rk + dr, generator=g).to(bf)                   # pool rows: [latent | shared key part]
+        kn = torch.randn(Tk, H, dn, generator=g).to(bf)
+        v = torch.randn(Tk, H, dv, generator=g).to(bf)
+        q = torch.randn(nq, H, dn + dr, generator=g).to(bf)
+        gate = (torch.randn(nq, H, generator=g) * 2).to(bf)
+        if window and nctx + nq // 2 - window + 1 >= 0:                      # loud key on the last position the window keeps
+            row, key = nq // 2, nctx + nq // 2 - window + 1
+            unit = torch.randn(dn + dr, generator=g)
+            unit = unit / unit.norm() * 9.0
+            q[row] = unit.to(bf)
+            kn[key] = unit[:dn].to(bf)
+            lat[key, Rk:] = unit[dn:].to(bf)
+        k = torch.cat([kn.double(), lat[:, None, Rk:].double().expand(Tk, H, dr)], -1)
+        want = R.windowed_attention(q.double(), k, v.double(), scale, window, first_pos=nctx)
+        wants.append(want * torch.sigmoid(gate.double())[:, :, None])
+        first = 0 if si % 2 else (max(0, nctx - window + 1) if window else 0)            # gather from the edge, or from 0
+        pool, bt = _paged(lat, bs, cuda, bf, si)
+        pools.append(pool), tables.append(bt), qs.append(q), gates.append(gate)
+        kns.append(kn[first:]), vs.append(v[first:])
+        cu_q.append(cu_q[-1] + nq), ctx.append(nctx), cu_k.append(cu_k[-1] + Tk - first), k_lo.append(first)
+    off, max_nb = 0, max(t.shape[0] for t in tables)
+    bts = torch.zeros(len(seqs), max_nb, dtype=torch.int32)
+    for i, (p, t) in enumerate(zip(pools, tables)):
+        bts[i, :t.shape[0]] = t + off
+        off += p.shape[0]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=cuda)          # noqa: E731
+    d_cu_k, d_k_lo = i32(cu_k), i32(k_lo)
+    lat_g = ops.latent_gather(torch.cat(pools), bts.to(cuda), d_cu_k, d_k_lo, len(seqs), cu_k[-1])
+    assert lat_g.shape == (cu_k[-1], Rk + dr)
+    qall = torch.cat(qs).to(cuda)
+    gate_wide = torch.cat([torch.zeros(cu_q[-1], 5, dtype=bf), torch.cat(gates)], 1).to(cuda)
+    got = ops.window_attention(qall[:, :, :dn], qall[:, :, dn:].contiguous(), torch.cat(kns).to(cuda).contiguous(), lat_g[:, Rk:],
+                               torch.cat(vs).to(cuda).contiguous(), i32(cu_q), i32(ctx), d_cu_k, d_k_lo, len(seqs), scale, window,
+                               gate=gate_wide[:, 5:])
+    _close(got, torch.cat(wants), bf, f"H={H} {dn}+{dr}/{dv} window={window}")
+
+
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("T,D,E,top", [(9, 48, 5, 2), (1, 64, 8, 8), (1500, 32, 3, 1), (40, 200, 40, 6)])
 def test_route_softmax_over_all_with_correction(cuda, dt, T, D, E, top):

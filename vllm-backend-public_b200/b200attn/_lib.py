@@ -130,6 +130,9 @@ SIGNATURES = {
     "b2_latent_prep": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp, vp, vp]),
     "b2_latent_attention": (i32, [vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp, i64, vp, i64,
                                   vp]),
+    "b2_latent_gather": (i32, [vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp]),
+    "b2_window_attention": (i32, [vp, vp, i64, i32, vp, i64, i32, vp, vp, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+                                  f32, i32, vp, i64, vp]),
     "b2_latent_attention_workspace": (i64, [i32, i32, i32, i32, i32, i32, i32, i32, i32]),
 }
 

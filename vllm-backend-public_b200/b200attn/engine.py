@@ -526,7 +526,7 @@ class LLMEngine:
             pf = PrefillBatch(cu_q=d_meta[B:B + npf + 1], ctx_start=d_meta[2 * B + 1:2 * B + 1 + npf],
                               block_tables=d_pbt, total_tokens=Tp,
                               kv_lens_host=(plan.prefill_start + plan.prefill_len).tolist(),
-                              state_slots=d_meta[4 * B + 1:4 * B + 1 + npf])
+                              state_slots=d_meta[4 * B + 1:4 * B + 1 + npf], q_lens_host=plan.prefill_len.tolist())
             logits = self.model.forward(d_tok, d_pos, d_slot, nd, dec_bt, dec_sl, pf, d_aux[B:B + max(ns, 1)], num_splits,
                                         dec_state_slots=d_meta[3 * B + 1:3 * B + 1 + nd])
             if want_rows is not None:

@@ -30,6 +30,11 @@ from . import ops
 
 ARCHITECTURE = "Gatolix"
 GLU_ALPHA = 1.702          # the design fixes the slope of the experts' gate sigmoid
+# A step with at least this many prompt rows rebuilds keys and values per head for them (bf16): (dim + rot_dim + vdim)
+# multiplications per (query, key, head) instead of (2 kv_rank + rot_dim) in the latent space, for two more GEMMs per layer
+# over the rows the portions can see.  Decode rows and short portions stay in the latent space.
+PROMPT_PER_HEAD_MIN_ROWS = 256
+PROMPT_PER_HEAD_MAX_CONTEXT = 4      # ... unless the visible rows outnumber the prompt rows by more than this factor
 
 
 @dataclass
@@ -293,11 +298,13 @@ class GatolixModel:
 
     def _fuse(self) -> None:
         """Per layer: one projection matrix for everything that reads the mixer's input (q | gate | down-projection),
-        the up-projections per head, stacked expert matrices."""
+        the gate's columns padded to a multiple of eight, the up-projections per head, stacked expert matrices."""
         w, c = self.w, self.cfg
         for i, L in enumerate(c.layer_specs):
             p, m, f = f"l{i}", L.mixer, L.mlp
-            parts = [w.pop(p + ".mix.q"), w.pop(p + ".mix.g")]
+            g = w.pop(p + ".mix.g")
+            pad = torch.zeros((-m.heads) % 8, g.shape[1], dtype=g.dtype, device=g.device)     # keeps what follows 16-byte aligned
+            parts = [w.pop(p + ".mix.q"), g, pad]
             if m.kv_from is None:
                 parts.append(w.pop(p + ".mix.dkv"))
             w[p + ".wproj"] = torch.cat(parts).contiguous()
@@ -336,22 +343,66 @@ class GatolixModel:
     def _ln(self, name: str):
         return self.w[name], self.w[name + ".b"]
 
-    def _mixer(self, li: int, h: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, batch: ops.SeqBatch) -> torch.Tensor:
+    def _prompt_plan(self, prefill) -> Optional[dict]:
+        """Host-side plan of the per-head path for the step's prompt portions: owner layer -> (rows N, cu_k, k_lo) of the
+        gathered pool rows, covering the widest window among the layers that read the pool.  None: the latent path."""
+        if prefill is None or self.dtype != torch.bfloat16 or prefill.total_tokens < PROMPT_PER_HEAD_MIN_ROWS \
+                or prefill.q_lens_host is None or prefill.kv_lens_host is None:
+            return None
+        specs = [L.mixer for L in self.cfg.layer_specs]
+        if not all(ops.window_attention_ok(self.dtype, m.dim, m.rot_dim, m.vdim) and m.row % 8 == 0 for m in specs):
+            return None
+        plan = {}
+        for o, mo in enumerate(specs):
+            if mo.kv_from is not None:
+                continue
+            windows = [m.window for i, m in enumerate(specs) if i == o or m.kv_from == o]
+            reach = 0 if 0 in windows else max(windows)
+            cu, lo = [0], []
+            for q, kv in zip(prefill.q_lens_host, prefill.kv_lens_host):
+                first = max(0, kv - q - (reach - 1)) if reach else 0
+                lo.append(first)
+                cu.append(cu[-1] + kv - first)
+            if cu[-1] > PROMPT_PER_HEAD_MAX_CONTEXT * prefill.total_tokens:
+                return None
+            meta = torch.tensor(cu + lo, dtype=torch.int32).to(self.dev, non_blocking=True)
+            plan[o] = (cu[-1], meta[:len(cu)], meta[len(cu):])
+        return plan
+
+    def _mixer(self, li: int, h: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, batch: ops.SeqBatch,
+               n_decode: int = 0, prefill=None, plan: Optional[dict] = None, gathered: Optional[dict] = None) -> torch.Tensor:
         m, w, p = self.cfg.layer_specs[li].mixer, self.w, f"l{li}"
         H, dn, dr, dv, R = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank
         T = h.shape[0]
-        proj = torch.nn.functional.linear(h, w[p + ".wproj"])                  # [T, H (dn + dr) | H | R + dr]
+        proj = torch.nn.functional.linear(h, w[p + ".wproj"])                  # [T, H (dn + dr) | H, padding | R + dr]
         g_off = H * (dn + dr)
+        d_off = g_off + H + (-H) % 8
         own = m.kv_from is None
-        cache = self.cache[li if own else m.kv_from]
-        qa = ops.latent_prep(proj, H, dn, dr, m.rot_dims, R, 0, g_off + H if own else -1, w.get(p + ".mix.dkv.norm"),
+        owner = li if own else m.kv_from
+        cache = self.cache[owner]
+        qa = ops.latent_prep(proj, H, dn, dr, m.rot_dims, R, 0, d_off if own else -1, w.get(p + ".mix.dkv.norm"),
                              self.cfg.eps, positions, self.rot[m.rot_key], slots if own else None, cache if own else None)
-        # the unrotated part of every query head, carried into the latent space: qa[:, h, :R] = q_h W_uk[h]
-        qn = proj[:, :g_off].view(T, H, dn + dr)[:, :, :dn].transpose(0, 1)    # [H, T, dn]
-        torch.bmm(qn, w[p + ".mix.uk"], out=qa[:, :, :R].transpose(0, 1))
-        o = ops.latent_attention(qa, cache, batch, R, m.scale, m.window, gate=proj[:, g_off:g_off + H])
+        qh = proj[:, :g_off].view(T, H, dn + dr)
+        gate = proj[:, g_off:g_off + H]
         ov = torch.empty(T, H, dv, dtype=h.dtype, device=h.device)
-        torch.bmm(o.transpose(0, 1), w[p + ".mix.uv"], out=ov.transpose(0, 1))   # head outputs = W_uv[h] (sum_j p_j c_j)
+        nl = T if plan is None else n_decode            # rows that stay in the latent space
+        if nl:
+            # the unrotated part of every query head, carried into the latent space: qa[:, h, :R] = q_h W_uk[h]
+            torch.bmm(qh[:nl, :, :dn].transpose(0, 1), w[p + ".mix.uk"], out=qa[:nl, :, :R].transpose(0, 1))
+            lb = batch if plan is None else ops.SeqBatch(batch.cu_q[:nl + 1], batch.ctx_start[:nl], batch.block_tables[:nl], None, nl, nl)
+            o = ops.latent_attention(qa[:nl], cache, lb, R, m.scale, m.window, gate=gate[:nl])
+            torch.bmm(o.transpose(0, 1), w[p + ".mix.uv"], out=ov[:nl].transpose(0, 1))   # head outputs = W_uv[h] (sum_j p_j c_j)
+        if plan is not None:
+            N, cu_k, k_lo = plan[owner]
+            npf = len(prefill.q_lens_host)
+            if owner not in gathered:                   # the owner has written this step's rows: gather once per pool
+                gathered[owner] = ops.latent_gather(cache, prefill.block_tables, cu_k, k_lo, npf, N)
+            lat = gathered[owner]
+            kn = torch.nn.functional.linear(lat[:, :R], w[p + ".mix.uk"].view(H * dn, R)).view(N, H, dn)
+            v = torch.empty(N, H, dv, dtype=h.dtype, device=h.device)
+            torch.bmm(lat[:, :R].unsqueeze(0).expand(H, N, R), w[p + ".mix.uv"], out=v.transpose(0, 1))
+            ov[nl:] = ops.window_attention(qh[nl:, :, :dn], qa[nl:, :, R:], kn, lat[:, R:], v, prefill.cu_q, prefill.ctx_start,
+                                           cu_k, k_lo, npf, m.scale, m.window, gate=gate[nl:])
         return torch.nn.functional.linear(ov.view(T, H * dv), w[p + ".mix.o"])
 
     def _mlp(self, li: int, h: torch.Tensor) -> torch.Tensor:
@@ -374,13 +425,15 @@ class GatolixModel:
         if n_decode and self._arange.shape[0] < n_decode + 1:
             self._arange = torch.arange(n_decode + 1, dtype=torch.int32, device=self.dev)
         batch = ops.step_batch(self._arange, n_decode, dec_block_tables, dec_seq_lens, None, prefill)
+        plan = self._prompt_plan(prefill)
+        gathered: Dict[int, torch.Tensor] = {}
         T, D = tokens.shape[0], c.hidden
         x = ops.embed_streams(w["embed"], tokens, 1, 1.0).view(T, D)            # the fp32 residual
         n = len(c.layer_specs)
         h = ops.sandwich_norm(x, None, None, None, *self._ln("l0.norm1"), eps=c.eps, h_dtype=self.dtype)
         for li in range(n):
             p = f"l{li}"
-            y = self._mixer(li, h, positions, slots, batch)
+            y = self._mixer(li, h, positions, slots, batch, n_decode, prefill, plan, gathered)
             post = self._ln(p + ".norm1b")
             if c.layer_specs[li].mlp is not None:
                 h = ops.sandwich_norm(x, y, *post, *self._ln(p + ".norm2"), eps=c.eps, h_dtype=self.dtype)

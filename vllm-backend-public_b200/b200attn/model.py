@@ -153,6 +153,7 @@ class PrefillBatch:
     total_tokens: int
     kv_lens_host: Optional[list] = None   # [ctx_start[c] + len_c] as host ints (fp8 cache: sizes the bf16 scratch)
     state_slots: Optional[torch.Tensor] = None   # int32 [n]: per-sequence state slot (models with recurrent state)
+    q_lens_host: Optional[list] = None    # rows of every chunk as host ints (models that plan per-chunk scratch on the host)
 
 
 class LlamaModel:

@@ -1079,3 +1079,58 @@ def latent_attention(qa: torch.Tensor, cache: torch.Tensor, batch: SeqBatch, R: 
                                        _ptr(batch.ctx_start), batch.n_seq, T, H, R, Dc - R, cache.shape[1], float(scale),
                                        int(window), _ptr(gate), gs, _ptr(ws), nws, _stream(dev)))
     return out
+
+
+def window_attention_ok(dtype: torch.dtype, dn: int, dr: int, dv: int) -> bool:
+    """Shapes b2_window_attention takes."""
+    return dtype == torch.bfloat16 and dn % 8 == 0 and dr % 8 == 0 and (dn + dr) % 16 == 0 and dn + dr > 0 and dv % 16 == 0 \
+        and 0 < dv <= 128
+
+
+def latent_gather(cache: torch.Tensor, block_tables: torch.Tensor, cu_k: torch.Tensor, k_lo: torch.Tensor, n_seq: int,
+                  N: int) -> torch.Tensor:
+    """Rows of the latent pool cache [nb, bs, Dc] that the step's prompt portions can see, as one buffer [N, Dc]: for
+    sequence i the positions k_lo[i] .. k_lo[i] + (cu_k[i+1] - cu_k[i]) - 1 at rows cu_k[i] ..  (int32 device tensors; N =
+    cu_k[n_seq], known on the host).  b2_latent_gather."""
+    lib = _lib.load()
+    dev = _need_cuda(cache=cache, block_tables=block_tables, cu_k=cu_k, k_lo=k_lo)
+    nb, bs, Dc = cache.shape
+    if cache.dtype != torch.bfloat16 or not cache.is_contiguous() or block_tables.dtype != torch.int32 or block_tables.dim() != 2 \
+            or (block_tables.shape[0] > 1 and block_tables.stride(0) != block_tables.shape[1]):
+        raise ValueError("cache must be contiguous bf16 [nb, bs, Dc], block_tables contiguous int32 [n, max_nb]")
+    out = torch.empty(N, Dc, dtype=cache.dtype, device=dev)
+    _lib.check(lib.b2_latent_gather(_ptr(out), _ptr(cache), _ptr(block_tables), block_tables.shape[1], _ptr(cu_k), _ptr(k_lo), n_seq,
+                                    N, bs, Dc, _stream(dev)))
+    return out
+
+
+def window_attention(qn: torch.Tensor, qr: torch.Tensor, kn: torch.Tensor, kt: torch.Tensor, v: torch.Tensor, cu_q: torch.Tensor,
+                     ctx_start: torch.Tensor, cu_k: torch.Tensor, k_lo: torch.Tensor, n_seq: int, scale: float, window: int = 0,
+                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sliding-window attention of prompt portions over keys and values held per head in gathered buffers.
+    qn [T, H, dn], qr [T, H, dr]: the two parts of the queries (views with a contiguous last axis); kn [N, H, dn], kt [N, dr]
+    (shared by the heads; may be a column slice), v [N, H, dv] over the gathered rows (see latent_gather).  The row at
+    position p sees positions max(0, p - window + 1) .. p (window 0: 0 .. p).  Returns sigmoid(gate[t, h]) * softmax(..) v as
+    bf16 [T, H, dv].  b2_window_attention."""
+    lib = _lib.load()
+    dev = _need_cuda(qn=qn, qr=qr, kn=kn, kt=kt, v=v, gate=gate)
+    T, H, dn = qn.shape
+    dr, dv, N = qr.shape[2], v.shape[2], kn.shape[0]
+    if tuple(qr.shape) != (T, H, dr) or tuple(kn.shape) != (N, H, dn) or tuple(kt.shape) != (N, dr) or tuple(v.shape) != (N, H, dv):
+        raise ValueError("qn [T, H, dn], qr [T, H, dr], kn [N, H, dn], kt [N, dr], v [N, H, dv]")
+    for name, t in (("qn", qn), ("qr", qr), ("kn", kn), ("kt", kt), ("v", v)):
+        if t.dtype != torch.bfloat16 or t.stride(-1) != 1:
+            raise ValueError(f"{name} must be bf16 with a contiguous last axis")
+    if not kn.is_contiguous() or not v.is_contiguous():
+        raise ValueError("kn and v must be contiguous")
+    gs = 0
+    if gate is not None:
+        if gate.dtype != torch.bfloat16 or tuple(gate.shape) != (T, H) or (H > 1 and gate.stride(1) != 1):
+            raise ValueError("gate must be bf16 [T, H] with a contiguous last axis")
+        gs = gate.stride(0) if T > 1 else H
+    out = torch.empty(T, H, dv, dtype=torch.bfloat16, device=dev)
+    _lib.check(lib.b2_window_attention(_ptr(out), _ptr(qn), qn.stride(0), qn.stride(1), _ptr(qr), qr.stride(0), qr.stride(1),
+                                       _ptr(kn), _ptr(kt), kt.stride(0), _ptr(v), _ptr(cu_q), _ptr(ctx_start), _ptr(cu_k),
+                                       _ptr(k_lo), n_seq, T, H, dn, dr, dv, float(scale), int(window), _ptr(gate), gs,
+                                       _stream(dev)))
+    return out

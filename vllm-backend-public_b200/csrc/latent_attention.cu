@@ -630,6 +630,206 @@ latent_attention_decode_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_
     }
 }
 
+// ------------------------------------------------------------------------------------------------- prompt portions, per-head keys
+// Long prompt portions are cheaper with keys and values rebuilt per head: a (query, key) pair then costs dn + dr + dv
+// multiplications instead of 2 R + dr.  The latent rows a portion can see are gathered from the pages into one
+// contiguous buffer per step (b2_latent_gather: for sequence i the positions k_lo[i] .. end, at rows cu_k[i] ..), the
+// per-head keys and values come from two library GEMMs over that buffer, and b2_window_attention runs over them:
+//   key of head h at gathered row g = [ kn[g, h, :dn] | kt[g, :dr] ]   (kt: the shared rotated part, a column slice of
+//   the gathered rows), value v[g, h, :dv]; query = [ qn[t, h, :dn] | qr[t, h, :dr] ] from two buffers as well.
+// One CTA = 64 consecutive rows of one sequence x one head, four warps of 16 rows, 64-key tiles staged through shared
+// memory, mma.sync m16n8k16 with ldmatrix operands, online softmax in registers (exp2, scale folded in).  bf16; dn and dr
+// multiples of 8, dn + dr and dv multiples of 16, dv <= 128.
+constexpr int kWQ = 64, kWK = 64, kWMaxDVT = 8;
+
+__global__ void latent_gather_kernel(const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables, int max_nb,
+                                     const int32_t* __restrict__ cu_k, const int32_t* __restrict__ k_lo, int n_seq, int bs, int Dc,
+                                     __nv_bfloat16* __restrict__ out) {
+    const int row = blockIdx.x;
+    const int seq = b2::seq_of_row(cu_k, n_seq, row);
+    const int j = k_lo[seq] + row - cu_k[seq];
+    const __nv_bfloat16* src = cache + ((size_t)block_tables[(size_t)seq * max_nb + j / bs] * bs + j % bs) * Dc;
+    __nv_bfloat16* dst = out + (size_t)row * Dc;
+    for (int c = threadIdx.x * 8; c < Dc; c += blockDim.x * 8) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+}
+
+__global__ void __launch_bounds__(128)
+window_attention_kernel(const __nv_bfloat16* __restrict__ qn, int64_t qn_row, int qn_head, const __nv_bfloat16* __restrict__ qr,
+                        int64_t qr_row, int qr_head, const __nv_bfloat16* __restrict__ kn, const __nv_bfloat16* __restrict__ kt,
+                        int64_t kt_row, const __nv_bfloat16* __restrict__ v, const int32_t* __restrict__ cu_q,
+                        const int32_t* __restrict__ ctx_start, const int32_t* __restrict__ cu_k, const int32_t* __restrict__ k_lo,
+                        int n_seq, int H, int dn, int dr, int dv, float scale_log2, int window,
+                        const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out) {
+    const int DK = dn + dr, LDK = DK + 8, LDV = dv + 8, dkt = DK / 16, dvt = dv / 16;
+    extern __shared__ __align__(16) unsigned char lat_smem[];
+    __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(lat_smem);       // [64][LDK]
+    __nv_bfloat16* k_sm = q_sm + kWQ * LDK;                                 // [64][LDK]
+    __nv_bfloat16* v_sm = k_sm + kWK * LDK;                                 // [64][LDV]
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    int seq = -1, t0 = 0;
+    {
+        int want = blockIdx.x;
+        for (int s = 0; s < n_seq; ++s) {
+            const int nt = (cu_q[s + 1] - cu_q[s] + kWQ - 1) / kWQ;
+            if (want < nt) { seq = s; t0 = want * kWQ; break; }
+            want -= nt;
+        }
+    }
+    if (seq < 0) return;
+    const int hh = blockIdx.y;
+    const int r0 = cu_q[seq] + t0;
+    const int rows = min(kWQ, cu_q[seq + 1] - r0);
+    const int ctx = ctx_start[seq];
+    if (ctx < 0) {
+        for (int idx = tid; idx < rows * (dv / 8); idx += 128)
+            *reinterpret_cast<uint4*>(out + ((size_t)(r0 + idx / (dv / 8)) * H + hh) * dv + (idx % (dv / 8)) * 8) = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    const int p0 = ctx + t0, p_last = p0 + rows - 1;
+    const int first = k_lo[seq];                                            // position of the sequence's first gathered row
+    const int klo = max(window > 0 ? max(p0 - window + 1, 0) : 0, first);
+    const size_t g0 = (size_t)cu_k[seq];
+
+    const int qv = DK / 8, nv8 = dn / 8;
+    for (int idx = tid; idx < kWQ * qv; idx += 128) {
+        const int r = idx / qv, c8 = idx % qv;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (r < rows) {
+            x = c8 < nv8 ? *reinterpret_cast<const uint4*>(qn + (size_t)(r0 + r) * qn_row + (size_t)hh * qn_head + c8 * 8)
+                         : *reinterpret_cast<const uint4*>(qr + (size_t)(r0 + r) * qr_row + (size_t)hh * qr_head + (c8 - nv8) * 8);
+        }
+        *reinterpret_cast<uint4*>(q_sm + r * LDK + c8 * 8) = x;
+    }
+    const int gq = lane >> 2, tq = lane & 3;
+    const int i0 = p0 + w * 16 + gq, i1 = i0 + 8;
+    const int lo0 = window > 0 ? max(i0 - window + 1, 0) : 0, lo1 = window > 0 ? max(i1 - window + 1, 0) : 0;
+    const int w_first = p0 + w * 16, w_last = w_first + 15;
+    const int w_lo = window > 0 ? max(w_first - window + 1, 0) : 0;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[2 * kWMaxDVT][4];
+#pragma unroll
+    for (int n = 0; n < 2 * kWMaxDVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const uint32_t q_base = b2::smem_u32(q_sm), k_base = b2::smem_u32(k_sm), v_base = b2::smem_u32(v_sm);
+    const int vv = dv / 8;
+
+    for (int kv0 = klo; kv0 <= p_last; kv0 += kWK) {
+        __syncthreads();                                                    // the previous tile is consumed (and Q is stored)
+        for (int idx = tid; idx < kWK * qv; idx += 128) {
+            const int key = idx / qv, c8 = idx % qv, j = kv0 + key;
+            __nv_bfloat16* dst = k_sm + key * LDK + c8 * 8;
+            if (j <= p_last) {
+                const size_t g = g0 + (size_t)(j - first);
+                cp_async16(dst, c8 < nv8 ? kn + (g * H + hh) * dn + c8 * 8 : kt + g * kt_row + (c8 - nv8) * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        for (int idx = tid; idx < kWK * vv; idx += 128) {
+            const int key = idx / vv, c8 = idx % vv, j = kv0 + key;
+            __nv_bfloat16* dst = v_sm + key * LDV + c8 * 8;
+            if (j <= p_last) cp_async16(dst, v + ((g0 + (size_t)(j - first)) * H + hh) * dv + c8 * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (kv0 > w_last || kv0 + kWK - 1 < w_lo) continue;                 // no key of the tile is visible to the warp's rows
+        float sc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll 2
+        for (int kk = 0; kk < dkt; ++kk) {
+            uint32_t a0, a1, a2, a3;
+            b2::ldmatrix_x4(q_base + 2u * ((w * 16 + (lane & 15)) * LDK + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                uint32_t b0, b1, b2_, b3;
+                const int key = n2 * 16 + (lane >> 4) * 8 + (lane & 7), dim = kk * 16 + ((lane >> 3) & 1) * 8;
+                b2::ldmatrix_x4(k_base + 2u * (key * LDK + dim), b0, b1, b2_, b3);
+                b2::mma_bf16_16816(sc[2 * n2], a0, a1, a2, a3, b0, b1);
+                b2::mma_bf16_16816(sc[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kv0 + n * 8 + 2 * tq + (e & 1);
+                const bool ok = e < 2 ? (j >= lo0 && j <= i0) : (j >= lo1 && j <= i1);
+                sc[n][e] = ok ? sc[n][e] * scale_log2 : -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = exp2f(m0 - mu0), c1 = exp2f(m1 - mu1);
+        m0 = mn0;
+        m1 = mn1;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            sc[n][0] = exp2f(sc[n][0] - mu0);
+            sc[n][1] = exp2f(sc[n][1] - mu0);
+            sc[n][2] = exp2f(sc[n][2] - mu1);
+            sc[n][3] = exp2f(sc[n][3] - mu1);
+            s0 += sc[n][0] + sc[n][1];
+            s1 += sc[n][2] + sc[n][3];
+        }
+        l0 = l0 * c0 + s0;
+        l1 = l1 * c1 + s1;
+#pragma unroll
+        for (int n = 0; n < 2 * kWMaxDVT; ++n) {
+            o[n][0] *= c0;
+            o[n][1] *= c0;
+            o[n][2] *= c1;
+            o[n][3] *= c1;
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t a0 = b2::pack_bf16x2(sc[2 * ks][0], sc[2 * ks][1]),
+                           a1 = b2::pack_bf16x2(sc[2 * ks][2], sc[2 * ks][3]);
+            const uint32_t a2 = b2::pack_bf16x2(sc[2 * ks + 1][0], sc[2 * ks + 1][1]),
+                           a3 = b2::pack_bf16x2(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < kWMaxDVT; ++n2) {
+                if (n2 < dvt) {
+                    uint32_t b0, b1, b2_, b3;
+                    const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = n2 * 16 + (lane >> 4) * 8;
+                    b2::ldmatrix_x4_trans(v_base + 2u * (key * LDV + col), b0, b1, b2_, b3);
+                    b2::mma_bf16_16816(o[2 * n2], a0, a1, a2, a3, b0, b1);
+                    b2::mma_bf16_16816(o[2 * n2 + 1], a0, a1, a2, a3, b2_, b3);
+                }
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int ra = w * 16 + gq, rb = ra + 8;
+    float f0 = l0 > 0.f ? 1.f / l0 : 0.f, f1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (gate) {
+        if (ra < rows) f0 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(r0 + ra) * gate_stride + hh]));
+        if (rb < rows) f1 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(r0 + rb) * gate_stride + hh]));
+    }
+#pragma unroll
+    for (int n = 0; n < 2 * kWMaxDVT; ++n) {
+        const int col = n * 8 + 2 * tq;
+        if (col < dv) {
+            if (ra < rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(r0 + ra) * H + hh) * dv + col) = b2::pack_bf16x2(o[n][0] * f0, o[n][1] * f0);
+            if (rb < rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(r0 + rb) * H + hh) * dv + col) = b2::pack_bf16x2(o[n][2] * f1, o[n][3] * f1);
+        }
+    }
+}
+
 // out[row, :] = gate * sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M) over the shares of a (token, head) row
 __global__ void latent_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, int nsplit, int R, int H,
                                     const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out) {
@@ -798,6 +998,45 @@ extern "C" int b2_latent_attention(void* out, const void* qa, const void* cache,
     B2_DISPATCH_ACT(act_dtype, A, (latent_attention_kernel<A><<<blocks, warps * 32, smem, st>>>(
         static_cast<const A*>(qa), static_cast<const A*>(cache), block_tables, max_nb, cu_q, ctx_start, n_seq, T, H, R, dr, bs,
         scale, window, static_cast<const A*>(gate), gate_stride, static_cast<A*>(out))));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_latent_gather(void* out, const void* cache, const int32_t* block_tables, int max_nb, const int32_t* cu_k,
+                                const int32_t* k_lo, int n_seq, int N, int bs, int Dc, void* stream) {
+    B2_REQUIRE(N >= 0 && n_seq >= 0 && bs > 0 && Dc > 0 && Dc % 8 == 0, B2_EINVAL, "latent_gather: bad sizes (row width %d)", Dc);
+    if (N == 0 || n_seq == 0) return B2_OK;
+    B2_REQUIRE(out && cache && block_tables && cu_k && k_lo && b2_aligned16(out) && b2_aligned16(cache), B2_EINVAL,
+               "latent_gather: null or unaligned pointer");
+    latent_gather_kernel<<<N, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(cache), block_tables, max_nb, cu_k, k_lo, n_seq, bs, Dc, static_cast<__nv_bfloat16*>(out));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_window_attention(void* out, const void* qn, int64_t qn_row, int qn_head, const void* qr, int64_t qr_row,
+                                   int qr_head, const void* kn, const void* kt, int64_t kt_row, const void* v,
+                                   const int32_t* cu_q, const int32_t* ctx_start, const int32_t* cu_k, const int32_t* k_lo,
+                                   int n_seq, int T, int H, int dn, int dr, int dv, float scale, int window, const void* gate,
+                                   int64_t gate_stride, void* stream) {
+    B2_REQUIRE(T >= 0 && n_seq >= 0 && H > 0 && dn >= 0 && dr >= 0 && dv > 0 && window >= 0, B2_EINVAL, "window_attention: bad sizes");
+    B2_REQUIRE(dn % 8 == 0 && dr % 8 == 0 && (dn + dr) % 16 == 0 && dn + dr > 0 && dv % 16 == 0 && dv <= 16 * kWMaxDVT, B2_EUNSUPPORTED,
+               "window_attention: head sizes %d + %d / %d", dn, dr, dv);
+    if (T == 0 || n_seq == 0) return B2_OK;
+    B2_REQUIRE(out && qn && qr && kn && kt && v && cu_q && ctx_start && cu_k && k_lo, B2_EINVAL, "window_attention: null pointer");
+    B2_REQUIRE(b2_aligned16(out) && b2_aligned16(qn) && b2_aligned16(qr) && b2_aligned16(kn) && b2_aligned16(kt) && b2_aligned16(v) &&
+                   qn_row % 8 == 0 && qn_head % 8 == 0 && qr_row % 8 == 0 && qr_head % 8 == 0 && kt_row % 8 == 0, B2_EINVAL,
+               "window_attention: pointers and strides must keep 16-byte alignment");
+    const size_t smem = (size_t)((kWQ + kWK) * (dn + dr + 8) + kWK * (dv + 8)) * sizeof(__nv_bfloat16);
+    B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "window_attention: key size %d too large", dn + dr);
+    if (smem > 48 * 1024)
+        B2_CUDA_OK(cudaFuncSetAttribute(window_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int tiles = T / kWQ + n_seq;
+    window_attention_kernel<<<dim3(tiles, H), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(qn), qn_row, qn_head, static_cast<const __nv_bfloat16*>(qr), qr_row, qr_head,
+        static_cast<const __nv_bfloat16*>(kn), static_cast<const __nv_bfloat16*>(kt), kt_row, static_cast<const __nv_bfloat16*>(v), cu_q,
+        ctx_start, cu_k, k_lo, n_seq, H, dn, dr, dv, scale * 1.4426950408889634f, window, static_cast<const __nv_bfloat16*>(gate),
+        gate_stride, static_cast<__nv_bfloat16*>(out));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
