@@ -219,14 +219,14 @@ def _kernels_gatolix(size, s, B, ctx, T):
         ms = _time(lambda: ops.rms_norm(y, wn, 1e-6, residual=res), flush)
         line("rms_norm (Llama, bf16 residual)", phase, ms, bytes_=rows * D * 2 * 4)
         # ---- rotation + pool write  |  like: rotary + KV write
-        P = H * (dn + dr) + H + Dc
+        P = H * (dn + dr) + H + (-H) % 8 + Dc
         proj = torch.randn(rows, P, device=dev).to(bf)
         pos = (torch.arange(rows, device=dev) % q_len + c).to(torch.int32)
         slots = (torch.arange(rows, device=dev) // q_len * (nb_seq * 16) + pos).to(torch.int64)
         cache = torch.randn(n_seq * nb_seq, 16, Dc, device=dev).to(bf)
         nw = torch.ones(R, device=dev)
         g_off = H * (dn + dr)
-        ms = _time(lambda: ops.latent_prep(proj, H, dn, dr, dr, R, 0, g_off + H, nw, 1e-6, pos, tab, slots, cache), flush)
+        ms = _time(lambda: ops.latent_prep(proj, H, dn, dr, dr, R, 0, g_off + H + (-H) % 8, nw, 1e-6, pos, tab, slots, cache), flush)
         line("latent_prep (rotation + norm + pool write)", phase, ms, bytes_=rows * (H * dr * 4 + Dc * 4), like="rope_and_cache")
         qkv = torch.randn(rows, (H + 2 * G) * d, device=dev).to(bf)
         kc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
@@ -253,9 +253,28 @@ def _kernels_gatolix(size, s, B, ctx, T):
         ms = _time(lambda: ops.latent_attention(qa, cache, batch, R, 0.07, W, gate=gate), flush)
         if phase == "prefill":
             pairs = sum(min(p + 1, W) for p in range(T))                       # visible (query, key) pairs per head
-            line("latent_attention (window %d)" % W, phase, ms, flops=2 * pairs * H * (Dc + R), like="prefill_attention")
-            q = torch.randn(rows, H, d, device=dev).to(bf)
+            line("latent_attention (window %d; portions below 256 rows)" % W, phase, ms, flops=2 * pairs * H * (Dc + R),
+                 like="prefill_attention")
+            # what the engine runs for a long portion instead: pool rows gathered, keys and values rebuilt per head
             cu, cs = i32([0, T]), i32([0])
+            ms = _time(lambda: ops.latent_gather(cache, tables, cu, cs, 1, T), flush)
+            line("latent_gather", phase, ms, bytes_=T * Dc * 4)
+            lat = ops.latent_gather(cache, tables, cu, cs, 1, T)
+            wukf = wuk.view(H * dn, R)
+            vbuf = torch.empty(T, H, dv, dtype=bf, device=dev)
+
+            def rebuild():
+                torch.nn.functional.linear(lat[:, :R], wukf)
+                torch.bmm(lat[:, :R].unsqueeze(0).expand(H, T, R), wuv, out=vbuf.transpose(0, 1))
+            ms = _time(rebuild, flush)
+            line("keys and values per head (2 cuBLAS GEMMs)", phase, ms, flops=2 * T * R * H * (dn + dv))
+            kn = torch.nn.functional.linear(lat[:, :R], wukf).view(T, H, dn)
+            qh = proj[:, :g_off].view(rows, H, dn + dr)
+            ms = _time(lambda: ops.window_attention(qh[:, :, :dn], qa[:, :, R:], kn, lat[:, R:], vbuf, cu, cs, cu, cs, 1, 0.07, W,
+                                                    gate=gate), flush)
+            line("window_attention (per-head keys, window %d)" % W, phase, ms, flops=2 * pairs * H * (dn + dr + dv),
+                 like="prefill_attention")
+            q = torch.randn(rows, H, d, device=dev).to(bf)
             ms = _time(lambda: ops.prefill_attention(q, kc, vc, tables, cu, cs, total_tokens=T), flush)
             line("prefill_attention (Llama, tcgen05, causal)", phase, ms, flops=4 * (T * (T + 1) // 2) * H * d)
         else:

@@ -11,8 +11,9 @@ vocabulary head are library GEMMs (torch -> cuBLAS); everything between them is 
 (csrc/post_norm.cu, latent_attention.cu, moe.cu).  There is no CPU path.
 
 Attention runs in the latent space: W_uk is applied to the query (one batched product per step) so that scores are
-taken against the cached rows directly, and W_uv is applied to the attention output; keys and values per head are never
-materialised, for prompts or for decoding.
+taken against the cached rows directly, and W_uv is applied to the attention output; keys and values per head are not
+materialised for decode rows and short portions.  A step with many prompt rows (bf16) rebuilds them per head for the
+pool rows its portions can see, which costs a third of the multiplications per (query, key) pair.
 
 Every size, the layer order and every constant come from the checkpoint's config.json (`architecture: "Gatolix"`);
 weights from its *.safetensors, or random from a seed.

@@ -653,7 +653,7 @@ __global__ void latent_gather_kernel(const __nv_bfloat16* __restrict__ cache, co
     for (int c = threadIdx.x * 8; c < Dc; c += blockDim.x * 8) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 window_attention_kernel(const __nv_bfloat16* __restrict__ qn, int64_t qn_row, int qn_head, const __nv_bfloat16* __restrict__ qr,
                         int64_t qr_row, int qr_head, const __nv_bfloat16* __restrict__ kn, const __nv_bfloat16* __restrict__ kt,
                         int64_t kt_row, const __nv_bfloat16* __restrict__ v, const int32_t* __restrict__ cu_q,
@@ -714,21 +714,22 @@ window_attention_kernel(const __nv_bfloat16* __restrict__ qn, int64_t qn_row, in
 
     for (int kv0 = klo; kv0 <= p_last; kv0 += kWK) {
         __syncthreads();                                                    // the previous tile is consumed (and Q is stored)
-        for (int idx = tid; idx < kWK * qv; idx += 128) {
-            const int key = idx / qv, c8 = idx % qv, j = kv0 + key;
-            __nv_bfloat16* dst = k_sm + key * LDK + c8 * 8;
+        {                                                                   // two threads per key row: one address, then 16-byte copies
+            const int key = tid >> 1, half = tid & 1, j = kv0 + key;
+            __nv_bfloat16* kd = k_sm + key * LDK;
+            __nv_bfloat16* vd = v_sm + key * LDV;
             if (j <= p_last) {
                 const size_t g = g0 + (size_t)(j - first);
-                cp_async16(dst, c8 < nv8 ? kn + (g * H + hh) * dn + c8 * 8 : kt + g * kt_row + (c8 - nv8) * 8);
+                const __nv_bfloat16* ks = kn + (g * H + hh) * dn;
+                const __nv_bfloat16* ts = kt + g * kt_row;
+                const __nv_bfloat16* vs = v + (g * H + hh) * dv;
+                for (int c8 = half; c8 < nv8; c8 += 2) cp_async16(kd + c8 * 8, ks + c8 * 8);
+                for (int c8 = half; c8 < qv - nv8; c8 += 2) cp_async16(kd + (nv8 + c8) * 8, ts + c8 * 8);
+                for (int c8 = half; c8 < vv; c8 += 2) cp_async16(vd + c8 * 8, vs + c8 * 8);
             } else {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                for (int c8 = half; c8 < qv; c8 += 2) *reinterpret_cast<uint4*>(kd + c8 * 8) = make_uint4(0, 0, 0, 0);
+                for (int c8 = half; c8 < vv; c8 += 2) *reinterpret_cast<uint4*>(vd + c8 * 8) = make_uint4(0, 0, 0, 0);
             }
-        }
-        for (int idx = tid; idx < kWK * vv; idx += 128) {
-            const int key = idx / vv, c8 = idx % vv, j = kv0 + key;
-            __nv_bfloat16* dst = v_sm + key * LDV + c8 * 8;
-            if (j <= p_last) cp_async16(dst, v + ((g0 + (size_t)(j - first)) * H + hh) * dv + c8 * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -737,7 +738,7 @@ window_attention_kernel(const __nv_bfloat16* __restrict__ qn, int64_t qn_row, in
         float sc[8][4];
 #pragma unroll
         for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-#pragma unroll 2
+#pragma unroll 4
         for (int kk = 0; kk < dkt; ++kk) {
             uint32_t a0, a1, a2, a3;
             b2::ldmatrix_x4(q_base + 2u * ((w * 16 + (lane & 15)) * LDK + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
